@@ -1,0 +1,392 @@
+"""Benchmark of the decode-layer hot path: microseconds per decoder layer.
+
+    python bench.py --gpus N --steps K --warmup W            # this library, N GPUs (tensor parallel)
+    python bench.py --impl reference --gpus N --steps K ...   # the CPU restatement on the host cores
+
+A step is one pass of one decoder layer's launch sequence over one batch of decode rows
+(default: the sparse-MLA FP8 MoE layer, 8 rows, tensor parallel over the N GPUs).  Layers
+with distinct weights are visited round-robin so every step streams its experts cold from
+HBM (one layer's picked experts are far larger than L2).  Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "us_per_decoder_layer"
+UNIT = "us"
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            p = json.load(fh)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        try:
+            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
+            os.unlink(self.path)
+            sm = [float(r[1]) for r in rows]
+            out["sm_mhz"] = statistics.median(sm) if sm else None
+            out["sm_max_mhz"] = float(rows[0][2]) if rows else None
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            seen = set()
+            for r in rows:
+                for nm, v in zip(names, r[5:9]):
+                    if v.strip().lower() == "active":
+                        seen.add(nm)
+            out["reasons"] = sorted(seen)
+            out["samples"] = len(rows)
+        except Exception:
+            pass
+        return out
+
+
+# --------------------------------------------------------------------------- workload
+def layer_cfg(rows: int, tp: int):
+    """Per-rank dimensions of the sparse-MLA FP8 MoE decoder layer at tensor-parallel size tp."""
+    return dict(rows=rows, tp=tp, hidden=7168, experts=256, topk=8, inter=2048 // tp, has_shared=True, score_fn=1,
+                route_scale=2.5, eps=1e-6, swiglu_limit=0.0)
+
+
+def make_layer_weights(cfg, seed: int, device):
+    """Random-init weights of one layer's MoE block in checkpoint layout, drawn on the device:
+    N(0, 0.02) quantised to e4m3 with 128x128 f32 block scales (block amax / 448)."""
+    g = torch.Generator(device=device).manual_seed(1000 * seed + 7)
+    H, E, I = cfg["hidden"], cfg["experts"], cfg["inter"]
+    n = E + 1
+
+    def qblock(rows_, cols_, count, chunk=8):
+        q = torch.empty(count, rows_, cols_, dtype=torch.float8_e4m3fn, device=device)
+        s = torch.empty(count, -(-rows_ // 128), cols_ // 128, device=device)
+        for e0 in range(0, count, chunk):
+            e1 = min(count, e0 + chunk)
+            w = 0.02 * torch.randn(e1 - e0, rows_, cols_, generator=g, device=device)
+            blk = w.view(e1 - e0, rows_ // 128, 128, cols_ // 128, 128)
+            amax = blk.abs().amax(dim=(2, 4), keepdim=True)
+            sc = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+            q[e0:e1] = (blk / sc).clamp(-448, 448).to(torch.float8_e4m3fn).view(e1 - e0, rows_, cols_)
+            s[e0:e1] = sc.view(e1 - e0, rows_ // 128, cols_ // 128)
+        return q, s
+
+    w13, w13_s = qblock(2 * I, H, n)
+    w2, w2_s = qblock(H, I, n)
+    return dict(
+        norm=(1 + 0.1 * torch.randn(H, generator=g, device=device)).to(torch.bfloat16),
+        gate_w=(0.02 * torch.randn(E, H, generator=g, device=device)).to(torch.bfloat16),
+        bias=(0.02 * torch.randn(E, generator=g, device=device)).float(),
+        w13=w13, w13_s=w13_s, w2=w2, w2_s=w2_s)
+
+
+def expert_bytes(cfg):
+    H, I = cfg["hidden"], cfg["inter"]
+    up = 2 * I * H + (-(-2 * I // 128)) * (H // 128) * 4
+    down = H * I + (H // 128) * (I // 128) * 4
+    return up, down
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    import sgl_amd_mono_b200  # noqa: F401
+    from sgl_amd_mono_b200 import cabi
+    from sgl_amd_mono_b200.ffn import FfnBuild, FfnRunner, FfnWeights
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tp = args.shard_of or world
+    cfg = layer_cfg(args.rows, tp)
+    lib = cabi.lib()
+
+    layers = []
+    for li in range(args.layers):
+        w = make_layer_weights(cfg, seed=li, device=dev)
+        b = FfnBuild(width=args.rows, hidden=cfg["hidden"], inter=cfg["inter"], experts=cfg["experts"], topk=cfg["topk"],
+                     score_fn=cfg["score_fn"], has_shared=True, route_scale=cfg["route_scale"], eps=cfg["eps"])
+        layers.append(FfnRunner(b, FfnWeights(norm=w["norm"], gate_w=w["gate_w"], bias=w["bias"], w13=w["w13"],
+                                              w13_s=w["w13_s"], w2=w["w2"], w2_s=w["w2_s"]), dev))
+    g = torch.Generator(device=dev).manual_seed(5)
+    n_in = 16
+    xs = [torch.randn(args.rows, cfg["hidden"], generator=g, device=dev).to(torch.bfloat16) for _ in range(n_in)]
+    res = torch.randn(args.rows, cfg["hidden"], generator=g, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(res)
+
+    # one CUDA graph per (layer, input): replay = one step, no host launch cost inside the timed region
+    stream = torch.cuda.Stream(dev)
+    graphs = []
+    with torch.cuda.stream(stream):
+        for li, r in enumerate(layers):
+            r.ffn(xs[li % n_in], out, res, True)  # warm caches / lazy init outside capture
+        stream.synchronize()
+        for i in range(max(args.layers, n_in)):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                layers[i % args.layers].ffn(xs[i % n_in], out, res, True)
+            graphs.append(gr)
+    launches_per_step = 5
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for i in range(steps):
+                fn(i)
+            e1.record(stream)
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    step = lambda i: graphs[i % len(graphs)].replay()  # noqa: E731
+    timed(step, args.warmup)
+    with ClockSampler(local) as cs:
+        ms = timed(step, args.steps)
+    clocks = cs.summary()
+    us_per_step = ms * 1000.0 / args.steps
+
+    # ---- end to end: host rows in, host rows out, every step, through the runner's public call
+    hx = [x.cpu().pin_memory() for x in xs]
+    hres = res.cpu().pin_memory()
+    hout = torch.empty_like(hres).pin_memory()
+    dx, dres = torch.empty_like(res), torch.empty_like(res)
+
+    def e2e_step(i):
+        dx.copy_(hx[i % n_in], non_blocking=True)
+        dres.copy_(hres, non_blocking=True)
+        layers[i % args.layers].ffn(dx, out, dres, True, stream=stream)
+        hout.copy_(out, non_blocking=True)
+        stream.synchronize()
+
+    timed(e2e_step, args.warmup)
+    e2e_us = timed(e2e_step, args.steps) * 1000.0 / args.steps
+    row_bytes = args.rows * cfg["hidden"] * 2
+
+    # ---- the dominant kernel (expert gate/up GEMV), timed alone over the same steps
+    up_b, down_b = expert_bytes(cfg)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    unions = []
+    with torch.cuda.stream(stream):
+        for i in range(args.steps):
+            r = layers[i % args.layers]
+            r.ffn(xs[i % n_in], out, res, True, stream=stream)  # fills this step's routing and xq
+            L = r.step_layout
+            sc = r.scratch
+            a = cabi.fill("B200MoeUpArgs", xq=sc[L.xq:], x_scale=sc[L.xs:], w13=r.w.w13, w13_scale=r.w.w13_s,
+                          union_count=sc[L.union_count:], union_ids=sc[L.union_ids:], mid=sc[L.mid:], rows=args.rows,
+                          hidden=cfg["hidden"], inter=cfg["inter"], experts=cfg["experts"], union_cap=L.union_cap,
+                          swiglu_limit=0.0)
+            # evict the weights the warm-up call above pulled into L2
+            flush = getattr(run_ours, "_flush", None)
+            if flush is None:
+                flush = run_ours._flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+            flush.zero_()
+            ev[i][0].record(stream)
+            lib.call("moe_up", a, stream.cuda_stream)
+            ev[i][1].record(stream)
+            unions.append(sc[L.union_count:L.union_count + 4].view(torch.int32).clone())
+        stream.synchronize()
+    up_us = [a.elapsed_time(b) * 1000.0 for a, b in ev]
+    u_mean = float(sum(int(u.item()) for u in unions)) / len(unions)
+    up_bytes = u_mean * up_b
+    peak, peak_kind = peaks()
+    up_gbs = up_bytes / (statistics.mean(up_us) * 1e-6) / 1e9
+    layer_bytes = u_mean * (up_b + down_b) + cfg["experts"] * cfg["hidden"] * 2
+
+    result = {
+        "metric": METRIC, "value": round(us_per_step, 3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(us_per_step / 1000.0, 6), "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate, bf16 rows)", "data": "synthetic",
+        "config": {
+            "workload": f"sparse-MLA FP8 MoE decoder layer, {args.rows} decode rows, TP{tp}: MoE FFN sub-block "
+                        "(RMSNorm+quant, router top-8 of 256, routed+shared experts); attention stages not in this line",
+            "rows": args.rows, "tp": tp, "layers_rotated": args.layers, "hidden": cfg["hidden"], "experts": 256, "topk": 8,
+            "inter_per_rank": cfg["inter"], "l2": "every step streams >1 GB of distinct expert weights (inputs larger than L2)",
+            "launch": "CUDA graph replay per step", "distinct_experts_per_step": u_mean,
+        },
+        "e2e": {"value": round(e2e_us, 3), "unit": UNIT, "h2d_bytes_per_step": 2 * row_bytes, "d2h_bytes_per_step": row_bytes},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+        "roofline": {
+            "bound": "hbm", "kernel": "gemv_kernel<2,NT> (expert gate/up GEMV + SwiGLU)", "achieved": round(up_gbs, 1),
+            "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(up_gbs / peak, 4), "traffic": None,
+            "bytes_per_launch": up_bytes, "us_per_launch": round(statistics.mean(up_us), 3),
+            "timed": "second pass over the same steps, CUDA events around the kernel on its stream, L2 flushed before each",
+            "step_bytes": layer_bytes, "step_frac_of_hbm_roofline": round(layer_bytes / (us_per_step * 1e-6) / 1e9 / peak, 4),
+        },
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        result["cpu_baseline"] = cpu_baseline(cfg, seconds=args.cpu_seconds)
+    if rank == 0:
+        print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- CPU arm
+class CpuBlock:
+    """The oracle's MoE block on the host cores.  Weights of `experts_sample` experts are drawn
+    once; a step times norm + router whole and the sampled experts, and scales the expert time
+    to the number of distinct experts the step's routing picked (+ the shared expert)."""
+
+    def __init__(self, cfg, experts_sample: int):
+        from oracle import quant as Q
+
+        self.cfg, self.n = cfg, experts_sample
+        g = torch.Generator().manual_seed(1)
+        H, I, E = cfg["hidden"], cfg["inter"], cfg["experts"]
+        self.xs = [torch.randn(cfg["rows"], H, generator=g).to(torch.bfloat16) for _ in range(4)]
+        self.norm = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+        self.gate = (0.02 * torch.randn(E, H, generator=g)).to(torch.bfloat16)
+        self.bias = (0.02 * torch.randn(E, generator=g)).numpy()
+        self.w13, self.w13_s = Q.quant_weight_block128(0.02 * torch.randn(experts_sample, 2 * I, H, generator=g))
+        self.w2, self.w2_s = Q.quant_weight_block128(0.02 * torch.randn(experts_sample, H, I, generator=g))
+
+    def step(self, i: int) -> float:
+        from oracle import moe as M
+        from oracle import quant as Q
+
+        cfg = self.cfg
+        t0 = time.perf_counter()
+        _, xn, xq, xs = M.rmsnorm_quant(self.xs[i % 4], self.norm, cfg["eps"])
+        logits = M.router_logits(xn, self.gate)
+        ids, _ = M.route(logits, self.bias, cfg["topk"], M.SCORE_SIGMOID_BIAS, cfg["route_scale"])
+        t_route = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        for e in range(self.n):
+            mid = M.expert_mid(xq, xs, self.w13[e], self.w13_s[e], 0.0)
+            mq, ms = Q.quant128(mid)
+            Q.gemv_fp8(mq, ms, self.w2[e], self.w2_s[e])
+        t_exp = (time.perf_counter() - t0) / self.n
+        self.distinct = len(set(ids.reshape(-1).tolist())) + 1
+        return (t_route + self.distinct * t_exp) * 1e6
+
+    def describe(self, steps: int) -> str:
+        return (f"{steps} steps; per step norm+router timed whole, {self.n} expert(s) timed and scaled to the "
+                f"step's distinct experts ({self.distinct})")
+
+
+def cpu_baseline(cfg, seconds: float = 15.0):
+    blk = CpuBlock(cfg, experts_sample=2)
+    blk.step(0)
+    vals, t0 = [], time.perf_counter()
+    while not vals or (time.perf_counter() - t0 < seconds and len(vals) < 50):
+        vals.append(blk.step(len(vals)))
+    return {"value": round(statistics.median(vals), 1), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": blk.describe(len(vals))}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tp = args.shard_of or args.gpus
+    cfg = layer_cfg(args.rows, tp)
+    blk = CpuBlock(cfg, experts_sample=1)
+    budget, t0, vals = 150.0, time.perf_counter(), []
+    for i in range(args.warmup + args.steps):
+        if vals and time.perf_counter() - t0 > budget:
+            break  # bounded: the remaining steps would repeat the same sample
+        v = blk.step(i)
+        if i >= args.warmup or args.warmup + args.steps <= 3:
+            vals.append(v)
+    if not vals:
+        vals.append(blk.step(0))
+    v = statistics.mean(vals)
+    base = {"value": round(v, 1), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": blk.describe(len(vals)) + (f"; stopped after {len(vals)} of {args.steps} timed steps (time bound)"
+                                                 if len(vals) < args.steps else "")}
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(v, 1), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(v / 1000.0, 3), "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8_e4m3 (dequantised, f64 accumulate)", "data": "synthetic",
+        "config": {"workload": f"sparse-MLA FP8 MoE decoder layer, {args.rows} decode rows, TP{tp}: MoE FFN sub-block, "
+                               "CPU restatement of the reference's torch goldens (the reference's own kernels are "
+                               "FlyDSL/ROCm-only and cannot run on this box)", "rows": args.rows, "tp": tp},
+        "cpu_baseline": base,
+        "e2e": {"value": round(v, 1), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=2, help="distinct-weight layers visited round-robin")
+    ap.add_argument("--shard-of", type=int, default=0, help="run rank 0's shard of a TP-<n> layer on one GPU (profiling)")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

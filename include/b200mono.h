@@ -1,0 +1,227 @@
+/* b200mono — C ABI of the B200 (sm_100a) decode-monokernel library.
+ *
+ * Every entry point takes one plain struct of device addresses and 32-bit
+ * integers plus the CUDA stream to launch on, exactly the shape in which the
+ * reference's host runner hands arguments to its compiled launches
+ * (`_run_compiled(launch, *ptrs, stream)`,
+ * sgl_amd_mono/deepseek_v41/gfx950/runner.py:687-738 and
+ * sgl_amd_mono/glm53/gfx950/runner.py:424-469: only 64-bit addresses and ints).
+ * No torch types, no exceptions, no allocation: the return value is 0 on
+ * success, a negative B200MONO_E_* code for a rejected argument, or a positive
+ * cudaError_t from the launch.  b200mono_last_error() returns the message of
+ * the calling thread's last failure.
+ *
+ * All pointers are device pointers valid on the current device unless a field
+ * says "host".  "e4m3" is FP8 E4M3 (finite, max 448), "bf16" is bfloat16.
+ * Matrices are row-major with the last dimension contiguous.
+ */
+#ifndef B200MONO_H_
+#define B200MONO_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MONO_ABI_VERSION 1
+
+enum {
+  B200MONO_OK = 0,
+  B200MONO_E_ARG = -1,      /* a size / alignment / null-pointer rule was violated */
+  B200MONO_E_SCRATCH = -2,  /* scratch buffer too small */
+  B200MONO_E_DEVICE = -3,   /* the current device is not sm_100 */
+  B200MONO_E_DEADLINE = -4  /* a device-side wait gave up (see the status words) */
+};
+
+/* Router score functions (reference: softmax top-k renormalised,
+ * test/kernels/test_qwen38_flash_next_launches.py:494-508; sigmoid + bias,
+ * sgl_amd_mono/glm53/check.py:172-197; sqrt(softplus) + bias,
+ * test/kernels/deepseek_v41/check_ffn.py:200-205). */
+enum {
+  B200MONO_SCORE_SOFTMAX = 0,
+  B200MONO_SCORE_SIGMOID_BIAS = 1,
+  B200MONO_SCORE_SQRT_SOFTPLUS_BIAS = 2
+};
+
+int b200mono_abi_version(void);
+const char* b200mono_last_error(void);
+/* 1 when the current CUDA device is compute capability 10.x, else 0. */
+int b200mono_device_ok(void);
+/* Number of SMs of the current device (persistent grids are sized from it). */
+int b200mono_sm_count(void);
+/* sizeof() of every argument struct below, in declaration order; returns how many
+ * there are.  A binding checks its own layouts against these at load time. */
+int b200mono_abi_sizes(int32_t* out, int32_t capacity);
+
+/* ------------------------------------------------------------------------
+ * Fused (residual add +) RMSNorm + per-128 FP8 activation quant.
+ * Replaces seam.stage_norm + store_x8
+ * (sgl_amd_mono/deepseek_v41/gfx950/stages/seam.py:331-384, layer.py:192-212)
+ * and _add_norm_quant_kernel (sgl_amd_mono/qwen35_a17b/fp8/gfx950/norm.py:26-63).
+ *   s = x (+ residual) in f32;  res_out = bf16(s)
+ *   y = bf16(s * (1/sqrt(mean(s^2) + eps)) * w)
+ *   per 128 columns: scale = max(amax|y|, 1e-10) / 448;  q = e4m3(clamp(y / scale))
+ */
+typedef struct {
+  const void* x;        /* bf16 [rows, hidden] */
+  const void* residual; /* bf16 [rows, hidden] or NULL */
+  const void* weight;   /* bf16 [hidden] */
+  void* res_out;        /* bf16 [rows, hidden] or NULL (only written with residual) */
+  void* y;              /* bf16 [rows, hidden] or NULL */
+  void* q;              /* e4m3 [rows, hidden] */
+  float* q_scale;       /* f32 [rows, hidden/128] */
+  int32_t rows, hidden; /* hidden % 128 == 0, hidden <= 16384 */
+  float eps;
+  int32_t gemma;        /* 1: multiply by (1 + w) instead of w */
+} B200NormQuantArgs;
+int b200mono_norm_quant(const B200NormQuantArgs* a, void* stream);
+
+/* Per-128 FP8 quant of bf16 rows (no norm): the re-quantisation of the SwiGLU
+ * output and of attention outputs before the next block-FP8 GEMV
+ * (sgl_amd_mono/qwen35_a17b/fp8/gfx950/gemv.py:256-266 `_quantize_rows`;
+ * sgl_amd_mono/glm53/check.py:416-424 `_q128`).  scale = amax > 0 ? amax/448 : 1
+ * when zero_rule == 1, else max(amax, 1e-10)/448. */
+typedef struct {
+  const void* x;   /* bf16 [rows, cols] */
+  void* q;         /* e4m3 [rows, cols] */
+  float* q_scale;  /* f32 [rows, cols/128] */
+  int32_t rows, cols;
+  int32_t zero_rule;
+} B200Quant128Args;
+int b200mono_quant128(const B200Quant128Args* a, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Weight-streaming block-FP8 GEMV for M <= 32 activation rows:
+ *   y[t, n] = sum_k  W[n,k] * ws[n/128, k/128] * xq[t, k] * xs[t, k/128]
+ * Replaces the q_a/kv_a, q_b, W_UK/W_UV, o_proj GEMV stages
+ * (sgl_amd_mono/deepseek_v41/gfx950/attention/front.py:161-476,
+ * attention/gemv.py:65-216; sgl_amd_mono/glm53/gfx950/kernel.py:1052-1515) and the
+ * Triton split-K GEMV (sgl_amd_mono/qwen35_a17b/fp8/gfx950/gemv.py:81-127).
+ * Activation rows are the MMA N dimension (swap-AB), weights are read once.
+ * `groups` > 1 makes the product block-diagonal: output rows
+ * [g*n/groups, (g+1)*n/groups) read input columns [g*k, (g+1)*k) of x (per-head
+ * absorbed W_UK / W_UV).
+ */
+typedef struct {
+  const void* w;        /* e4m3 [n, k] */
+  const float* w_scale; /* f32 [ceil(n/128), k/128] */
+  const void* xq;       /* e4m3 [rows, groups*k] */
+  const float* x_scale; /* f32 [rows, groups*k/128] */
+  void* y;              /* bf16 [rows, ldy] (or f32 when y_f32) */
+  int32_t rows;         /* 1..32 */
+  int32_t n, k;         /* n % 16 == 0, k % 128 == 0 */
+  int32_t groups;       /* >= 1, n % (16*groups) == 0 */
+  int32_t ldy;          /* elements between output rows (>= n) */
+  int32_t y_f32;        /* 1: y is f32 */
+} B200GemvFp8Args;
+int b200mono_gemv_fp8(const B200GemvFp8Args* a, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Router: bf16 gate GEMV in a fixed summation order, score function, exact
+ * top-k (ties -> smaller expert id), weights, and the union of picked experts.
+ * Replaces stage_router/stage_route (sgl_amd_mono/deepseek_v41/gfx950/stages/moe.py:267-390)
+ * and route_top8 (sgl_amd_mono/glm53/gfx950/kernel.py:1926-1999).
+ * Order of the f32 logit sum for (row t, expert e): lane l of a warp adds the
+ * products of columns 8*(l + 32*i) + j for i = 0.., j = 0..7 in that order;
+ * the 32 lane sums meet in an xor tree (16, 8, 4, 2, 1).
+ */
+typedef struct {
+  const void* x;          /* bf16 [rows, hidden] (the normed activations) */
+  const void* gate_w;     /* bf16 [experts, hidden] */
+  const float* bias;      /* f32 [experts] or NULL (selection bias) */
+  float* logits;          /* f32 [rows, experts] out */
+  int32_t* topk_ids;      /* int32 [rows, topk] out, in rank order */
+  float* topk_w;          /* f32 [rows, topk] out */
+  int32_t* union_count;   /* int32 [1] out: distinct picked experts U (+1 if shared) */
+  int32_t* union_ids;     /* int32 [experts+1] out: ascending expert ids, shared last */
+  uint8_t* union_pick;    /* u8 [experts+1, 32] out: slot+1 of row t in union entry u, 0 = not picked */
+  uint32_t* counter;      /* u32 [1], zero before the first launch; self-resetting */
+  int32_t rows, hidden, experts, topk;
+  int32_t score_fn;       /* B200MONO_SCORE_* */
+  float route_scale;
+  int32_t has_shared;     /* 1: append expert id `experts` as a last union entry picked by every row in slot topk */
+} B200RouterArgs;
+int b200mono_router(const B200RouterArgs* a, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Routed + shared experts, block-FP8 (128x128 f32 scales) weights.
+ * Replaces stage_shared/stage_ug/stage_down/down_combine
+ * (sgl_amd_mono/deepseek_v41/gfx950/stages/moe.py:509-1227) and
+ * sgl_amd_mono/glm53/gfx950/kernel.py:5662-7150.  Every distinct picked expert
+ * is streamed once; all rows ride along as MMA columns.
+ *   up:   h = W13[e] xq;  mid = bf16(silu(min(g, L)) * clamp(u, -L, L))  (L <= 0: no clamp)
+ *   down: y = W2[e] midq; out[t] = sum over slots in slot order of bf16(y * w), bf16 at each add,
+ *         shared expert last with weight 1.
+ */
+typedef struct {
+  const void* xq;           /* e4m3 [rows, hidden] */
+  const float* x_scale;     /* f32 [rows, hidden/128] */
+  const void* w13;          /* e4m3 [experts(+1), 2*inter, hidden]: gate rows then up rows */
+  const float* w13_scale;   /* f32 [experts(+1), 2*inter/128, hidden/128] */
+  const int32_t* union_count;
+  const int32_t* union_ids;
+  void* mid;                /* bf16 [union_cap, rows, inter] out (first U entries used) */
+  int32_t rows, hidden, inter, experts;
+  int32_t union_cap;        /* upper bound of U the grid is sized for: min(rows*topk, experts) + 1 */
+  float swiglu_limit;
+} B200MoeUpArgs;
+int b200mono_moe_up(const B200MoeUpArgs* a, void* stream);
+
+typedef struct {
+  const void* midq;         /* e4m3 [union_cap, rows, inter] */
+  const float* mid_scale;   /* f32 [union_cap, rows, inter/128] */
+  const void* w2;           /* e4m3 [experts(+1), hidden, inter] */
+  const float* w2_scale;    /* f32 [experts(+1), hidden/128, inter/128] */
+  const int32_t* union_count;
+  const int32_t* union_ids;
+  const uint8_t* union_pick;
+  const float* topk_w;      /* f32 [rows, topk] */
+  const void* residual;     /* bf16 [rows, hidden] or NULL: added in f32 before the final rounding */
+  void* out;                /* bf16 [rows, hidden] */
+  int32_t rows, hidden, inter, experts, topk;
+} B200MoeDownArgs;
+int b200mono_moe_down(const B200MoeDownArgs* a, void* stream);
+
+/* ------------------------------------------------------------------------
+ * The whole MoE FFN block as one call (norm -> quant -> router -> experts):
+ * the counterpart of the reference's standalone FFN launch
+ * (sgl_amd_mono/deepseek_v41/gfx950/layer.py:852-882, runner `ffn`,
+ * runner.py:266-856).  Intermediates live in `scratch` at the offsets
+ * b200mono_moe_ffn_layout() reports, so a checker can read the launch's own
+ * normed rows, logits, routing and mid values.
+ */
+typedef struct {
+  int64_t res, xn, xq, xs, logits, topk_ids, topk_w, union_count, union_ids, union_pick, counter,
+      mid, midq, mids, total;
+  int32_t union_cap, pad_;
+} B200MoeFfnLayout;
+int b200mono_moe_ffn_layout(int32_t rows, int32_t hidden, int32_t inter, int32_t experts,
+                            int32_t topk, B200MoeFfnLayout* out);
+
+typedef struct {
+  const void* x;          /* bf16 [rows, hidden] */
+  const void* residual;   /* bf16 [rows, hidden] or NULL; with it the block computes on s = x + residual */
+  void* out;              /* bf16 [rows, hidden]: MoE(s_normed) (+ s when add_residual) */
+  const void* norm_w;     /* bf16 [hidden] */
+  const void* gate_w;     /* bf16 [experts, hidden] */
+  const float* gate_bias; /* f32 [experts] or NULL */
+  const void* w13;
+  const float* w13_scale;
+  const void* w2;
+  const float* w2_scale;
+  void* scratch;          /* >= layout.total bytes, 256-byte aligned; counter word zeroed once */
+  int64_t scratch_bytes;
+  int32_t rows, hidden, inter, experts, topk;
+  int32_t score_fn;
+  int32_t has_shared;
+  int32_t add_residual;   /* 1: out = bf16(moe + s) */
+  float eps, route_scale, swiglu_limit;
+} B200MoeFfnArgs;
+int b200mono_moe_ffn(const B200MoeFfnArgs* a, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MONO_H_ */

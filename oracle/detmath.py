@@ -1,0 +1,63 @@
+"""Defined f32 arithmetic: every operation is one IEEE-754 binary32 operation in a
+stated order, so the CUDA kernels (which spell the same operations with
+``__fadd_rn`` / ``__fmul_rn`` / ``__fdiv_rn`` / ``__fsqrt_rn``) and this file
+produce the same bits.  Routing decisions depend on these bits, which is why the
+kernels do not call ``expf``: its rounding is not specified.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+F = np.float32
+
+
+def f32(x) -> np.ndarray:
+    return np.asarray(x, dtype=np.float32)
+
+
+def det_exp(x) -> np.ndarray:
+    """exp(x): n = rint(x*log2e); r = x - n*ln2_hi - n*ln2_lo; degree-6 Horner; scale by 2^n in two steps."""
+    x = np.minimum(np.maximum(f32(x), F(-87.0)), F(88.0))
+    n = np.rint(x * F(1.4426950408889634))
+    r = x - n * F(0.693145751953125)
+    r = r - n * F(1.428606765330187e-06)
+    p = np.full_like(r, F(1.3888889225e-03))
+    for c in (8.3333337680e-03, 4.1666667908e-02, 1.6666667163e-01, 0.5, 1.0, 1.0):
+        p = p * r + F(c)
+        p = p.astype(np.float32)
+    e = n.astype(np.int32)
+    e1 = np.trunc(e / 2).astype(np.int32)  # C integer division truncates toward zero
+    e2 = e - e1
+    s1 = ((e1 + 127) << 23).astype(np.int32).view(np.float32)
+    s2 = ((e2 + 127) << 23).astype(np.int32).view(np.float32)
+    return ((p * s1).astype(np.float32) * s2).astype(np.float32)
+
+
+def det_sigmoid(x) -> np.ndarray:
+    return (F(1.0) / (F(1.0) + det_exp(-f32(x)))).astype(np.float32)
+
+
+def det_silu(x) -> np.ndarray:
+    x = f32(x)
+    return (x * det_sigmoid(x)).astype(np.float32)
+
+
+def det_rsqrt(x) -> np.ndarray:
+    return (F(1.0) / np.sqrt(f32(x))).astype(np.float32)
+
+
+def warp_sum_tree(v: np.ndarray) -> np.ndarray:
+    """Xor tree (16, 8, 4, 2, 1) over the last axis of 32 lanes; returns the lane-0 value."""
+    assert v.shape[-1] == 32 and v.dtype == np.float32
+    idx = np.arange(32)
+    for off in (16, 8, 4, 2, 1):
+        v = (v + v[..., idx ^ off]).astype(np.float32)
+    return v[..., 0]
+
+
+def radix_key(x) -> np.ndarray:
+    """Order-preserving uint32 image of f32 bits: larger float <=> larger key
+    (sgl_amd_mono/glm53/check.py:111-114 `_radix_keys`; glm53/gfx950/kernel.py:3591-3592)."""
+    b = f32(x).view(np.uint32)
+    return np.where(b & np.uint32(0x80000000), ~b, b ^ np.uint32(0x80000000)).astype(np.uint32)

@@ -1,0 +1,182 @@
+"""RMSNorm + quant, router and MoE FFN block (routed + shared experts).
+
+Summation orders that decide a routing bit are restated exactly (numpy f32, one
+rounding per operation); GEMV results that only enter a tolerance check use
+f64 accumulation of the dequantised operands.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import detmath as dm
+from . import quant as Q
+
+SCORE_SOFTMAX, SCORE_SIGMOID_BIAS = 0, 1
+
+
+def _np(x: torch.Tensor) -> np.ndarray:
+    return x.detach().cpu().float().contiguous().numpy()
+
+
+def rmsnorm_quant(x, weight, eps, residual=None, gemma=False):
+    """(s bf16, y bf16, q e4m3, scale f32 [rows, H/128]).
+
+    s = x (+ residual) in f32, y = bf16(s * rstd * w), rstd = 1/sqrt(mean(s^2)+eps)
+    (sgl_amd_mono/qwen35_a17b/fp8/gfx950/norm.py:45-62; sgl_amd_mono/glm53/check.py:391-393).
+    Order of the sum of squares: thread i of 256 adds the squares of the 8-column
+    vectors i, i+256, .. in column order; 32 lanes meet in an xor tree; the 8 warp
+    sums are added in warp order.
+    """
+    rows, hidden = x.shape
+    s = _np(x)
+    if residual is not None:
+        s = (s + _np(residual)).astype(np.float32)
+    nvec = hidden // 8
+    per = -(-nvec // 256)
+    sq = np.zeros((rows, per * 256 * 8), np.float32)
+    sq[:, :hidden] = (s * s).astype(np.float32)
+    sq = sq.reshape(rows, per, 256, 8)
+    acc = np.zeros((rows, 256), np.float32)
+    for i in range(per):
+        for j in range(8):
+            acc = (acc + sq[:, i, :, j]).astype(np.float32)
+    warp = dm.warp_sum_tree(acc.reshape(rows, 8, 32))
+    tot = warp[:, 0]
+    for w in range(1, 8):
+        tot = (tot + warp[:, w]).astype(np.float32)
+    var = (tot / np.float32(hidden)).astype(np.float32)
+    rstd = dm.det_rsqrt((var + np.float32(eps)).astype(np.float32))
+    wf = _np(weight)
+    if gemma:
+        wf = (np.float32(1.0) + wf).astype(np.float32)
+    y = ((s * rstd[:, None]).astype(np.float32) * wf[None, :]).astype(np.float32)
+    y = torch.from_numpy(y).to(torch.bfloat16)
+    q, scale = Q.quant128(y, zero_rule=False)
+    return torch.from_numpy(s).to(torch.bfloat16), y, q, scale
+
+
+def router_logits(xn: torch.Tensor, gate_w: torch.Tensor) -> np.ndarray:
+    """f32 logits [rows, E] in the kernel's order: lane l of 32 adds the products of
+    columns 8*(l + 32 i) + j, i ascending, j = 0..7; then the xor tree.
+    (The reference fixes its own order the same way: K parts summed in wave order,
+    sgl_amd_mono/deepseek_v41/gfx950/stages/router.py:1-6.)"""
+    x, w = _np(xn), _np(gate_w)
+    rows, hidden = x.shape
+    E = w.shape[0]
+    nvec = hidden // 8
+    per = -(-nvec // 32)
+    out = np.empty((rows, E), np.float32)
+    wp = np.zeros((E, per * 32 * 8), np.float32)
+    wp[:, :hidden] = w
+    wp = wp.reshape(E, per, 32, 8)
+    for t in range(rows):
+        xp = np.zeros(per * 32 * 8, np.float32)
+        xp[:hidden] = x[t]
+        xp = xp.reshape(per, 32, 8)
+        acc = np.zeros((E, 32), np.float32)
+        for i in range(per):
+            for j in range(8):
+                acc = (acc + (wp[:, i, :, j] * xp[None, i, :, j]).astype(np.float32)).astype(np.float32)
+        out[t] = dm.warp_sum_tree(acc)
+    return out
+
+
+def route(logits: np.ndarray, bias, topk: int, score_fn: int, route_scale: float):
+    """(ids int32 [rows, k] in rank order, weights f32 [rows, k]).
+
+    Selection by (key descending, expert id ascending) on the radix key of the f32
+    selection value: the logit for softmax (monotone in the probability), or
+    sigmoid(logit) + bias.  Weights: softmax over the picked logits (= softmax top-k
+    renormalised, test/kernels/test_qwen38_flash_next_launches.py:497-499), or
+    sigmoid / sum * scale (sgl_amd_mono/glm53/check.py:184-195), sums in rank order."""
+    logits = np.asarray(logits, np.float32)
+    rows, E = logits.shape
+    if score_fn == SCORE_SOFTMAX:
+        score = logits
+        sel = logits
+    else:
+        score = dm.det_sigmoid(logits)
+        sel = score if bias is None else (score + np.asarray(bias, np.float32)[None, :]).astype(np.float32)
+    key = dm.radix_key(sel).astype(np.int64)
+    order = np.lexsort((np.arange(E)[None, :].repeat(rows, 0), -key), axis=-1)[:, :topk]
+    ids = order.astype(np.int32)
+    raw = np.take_along_axis(score, order, 1).astype(np.float32)
+    if score_fn == SCORE_SOFTMAX:
+        wgt = dm.det_exp((raw - raw[:, :1]).astype(np.float32))
+    else:
+        wgt = raw
+    tot = np.zeros(rows, np.float32)
+    for k in range(topk):
+        tot = (tot + wgt[:, k]).astype(np.float32)
+    wgt = (wgt / tot[:, None]).astype(np.float32)
+    if score_fn != SCORE_SOFTMAX:
+        wgt = (wgt * np.float32(route_scale)).astype(np.float32)
+    return ids, wgt
+
+
+def union_of(ids: np.ndarray, experts: int, has_shared: bool):
+    """Ascending distinct picked ids (+ the shared expert id `experts` last) and pick[u][t] = slot+1."""
+    rows, k = ids.shape
+    uni = sorted(set(ids.reshape(-1).tolist()))
+    pick = np.zeros((len(uni) + (1 if has_shared else 0), 32), np.uint8)
+    pos = {e: i for i, e in enumerate(uni)}
+    for t in range(rows):
+        for s in range(k):
+            pick[pos[int(ids[t, s])], t] = s + 1
+    if has_shared:
+        pick[len(uni), :rows] = k + 1
+        uni = uni + [experts]
+    return np.asarray(uni, np.int32), pick
+
+
+def expert_mid(xq, xs, w13, w13_s, limit: float) -> torch.Tensor:
+    """bf16 SwiGLU output of one expert for all rows: h = W13 xq, mid = bf16(silu(min(g,L)) * clamp(u,+-L))
+    (test/kernels/deepseek_v41/check_ffn.py:214-216; no clamp when L <= 0 as
+    sgl_amd_mono/glm53/gfx950/kernel.py:5715-5724)."""
+    inter = w13.shape[0] // 2
+    h = Q.gemv_fp8(xq, xs, w13, w13_s)
+    g, u = h[:, :inter], h[:, inter:]
+    if limit > 0:
+        g = g.clamp(max=limit)
+        u = u.clamp(-limit, limit)
+    return (torch.nn.functional.silu(g) * u).to(torch.bfloat16)
+
+
+def moe_ffn(x, w, cfg, residual=None, add_residual=False, route_from=None):
+    """The MoE FFN block; returns a dict of every intermediate the kernel exposes.
+
+    w: dict(norm, gate_w, bias|None, w13, w13_s, w2, w2_s) with expert-major tensors whose
+    last entry is the shared expert when cfg['has_shared'].  Routed sum in slot order with a
+    bf16 rounding at each add, shared expert last
+    (test/kernels/deepseek_v41/check_ffn.py:219-229; sgl_amd_mono/deepseek_v41/gfx950/stages/moe.py:1166-1173).
+    route_from: optional bf16 normed rows to route on (a launch's own rows)."""
+    rows, hidden = x.shape
+    E, k = cfg["experts"], cfg["topk"]
+    x = x.cpu()
+    residual = None if residual is None else residual.cpu()
+    s, xn, xq, xs = rmsnorm_quant(x, w["norm"], cfg["eps"], residual)
+    logits = router_logits(xn if route_from is None else route_from, w["gate_w"])
+    bias = None if w.get("bias") is None else _np(w["bias"])
+    ids, wts = route(logits, bias, k, cfg["score_fn"], cfg.get("route_scale", 1.0))
+    uni, pick = union_of(ids, E, cfg["has_shared"])
+    mids = {}
+    per_slot = torch.zeros(k + 1, rows, hidden)
+    for u, e in enumerate(uni.tolist()):
+        mid = expert_mid(xq, xs, w["w13"][e], w["w13_s"][e], cfg.get("swiglu_limit", 0.0))
+        mids[e] = mid
+        mq, ms = Q.quant128(mid, zero_rule=False)
+        y = Q.gemv_fp8(mq, ms, w["w2"][e], w["w2_s"][e])
+        for t in range(rows):
+            sl = int(pick[u, t])
+            if sl:
+                wgt = float(wts[t, sl - 1]) if sl <= k else 1.0
+                per_slot[sl - 1, t] = Q.bf(y[t] * np.float32(wgt))
+    acc = torch.zeros(rows, hidden)
+    for sl in range(k + (1 if cfg["has_shared"] else 0)):
+        acc = Q.bf(acc + per_slot[sl])
+    if add_residual:
+        acc = Q.bf(acc + s.float())
+    return dict(s=s, xn=xn, xq=xq, xs=xs, logits=logits, ids=ids, wts=wts, union=uni, pick=pick,
+                mids=mids, out=acc.to(torch.bfloat16))

@@ -1,0 +1,148 @@
+"""Quantisation rules of the hot path (torch CPU, f32 arithmetic).
+
+Each rule follows a reference torch golden; the CUDA kernels must reproduce the
+codes bit for bit when fed the same bf16 rows.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+FP8_MAX = 448.0
+BLOCK = 128
+E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def bf(x: torch.Tensor) -> torch.Tensor:
+    """Round to bf16 and come back to f32 (test/kernels/deepseek_v41/check_ffn.py:122-123)."""
+    return x.to(torch.bfloat16).float()
+
+
+def to_e4m3(x: torch.Tensor) -> torch.Tensor:
+    """Saturating RNE conversion to e4m3 (values are clamped first: the format has no inf)."""
+    return x.float().clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+
+
+def quant128(x: torch.Tensor, zero_rule: bool = False):
+    """bf16 rows -> (e4m3 [.., K], f32 scales [.., K/128]).
+
+    zero_rule False: scale = max(amax, 1e-10)/448 (sgl_amd_mono/qwen35_a17b/fp8/gfx950/norm.py:58-62).
+    zero_rule True : scale = amax/448, 1 when amax == 0 (sgl_amd_mono/qwen35_a17b/fp8/gfx950/gemv.py:256-266,
+    sgl_amd_mono/glm53/check.py:416-424).  q = e4m3(clamp(x / scale)).
+    """
+    shp = x.shape
+    g = x.float().reshape(*shp[:-1], shp[-1] // BLOCK, BLOCK)
+    amax = g.abs().amax(-1, keepdim=True)
+    if zero_rule:
+        scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    else:
+        scale = amax.clamp_min(1e-10) / FP8_MAX
+    q = to_e4m3(g / scale).reshape(shp)
+    return q, scale.squeeze(-1).contiguous()
+
+
+def dequant128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    shp = q.shape
+    return (q.float().reshape(*shp[:-1], -1, BLOCK) * scale.float().unsqueeze(-1)).reshape(shp)
+
+
+def quant_weight_block128(w: torch.Tensor):
+    """f32/bf16 weights [.., N, K] -> (e4m3 [.., N, K], f32 [.., ceil(N/128), K/128]) with
+    scale = block amax / 448 (1 for an all-zero block): the checkpoint format the
+    reference reads (sgl_amd_mono/glm53/check.py:427-432 `slices_f32` is its inverse)."""
+    *lead, n, k = w.shape
+    nb, kb = -(-n // BLOCK), k // BLOCK
+    wp = torch.zeros(*lead, nb * BLOCK, k, dtype=torch.float32, device=w.device)
+    wp[..., :n, :] = w.float()
+    blk = wp.reshape(*lead, nb, BLOCK, kb, BLOCK)
+    amax = blk.abs().amax(dim=(-3, -1), keepdim=True)
+    scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    q = to_e4m3(blk / scale).reshape(*lead, nb * BLOCK, k)[..., :n, :].contiguous()
+    return q, scale.reshape(*lead, nb, kb).contiguous()
+
+
+def deq_weight_block128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """(sgl_amd_mono/glm53/check.py:427-432; sgl_amd_mono/qwen35_a17b/fp8/gfx950/gemv.py:268-273)."""
+    n, k = q.shape[-2:]
+    s = scale.float().repeat_interleave(BLOCK, -2).repeat_interleave(BLOCK, -1)
+    return q.float() * s[..., :n, :k]
+
+
+def gemv_fp8(xq, xs, wq, ws, groups: int = 1) -> torch.Tensor:
+    """f32 result of the block-FP8 GEMV on already-quantised activations
+    (sgl_amd_mono/qwen35_a17b/fp8/gfx950/gemv.py:268-273 `_plain_gemv`), f64 accumulation."""
+    x = dequant128(xq.cpu(), xs.cpu()).double()
+    w = deq_weight_block128(wq.cpu(), ws.cpu()).double()
+    n, k = w.shape
+    if groups == 1:
+        return (x @ w.T).float()
+    rows_g = n // groups
+    out = torch.empty(x.shape[0], n, dtype=torch.float64)
+    for g in range(groups):
+        out[:, g * rows_g : (g + 1) * rows_g] = x[:, g * k : (g + 1) * k] @ w[g * rows_g : (g + 1) * rows_g].T
+    return out.float()
+
+
+# ----------------------------------------------------------------------------- MX formats
+def e8m0_value(code: torch.Tensor) -> torch.Tensor:
+    """2^(code-127) (sgl_amd_mono/common/mx.py:15-18)."""
+    return torch.exp2(code.float() - 127.0)
+
+
+def code_ceil(v: torch.Tensor) -> torch.Tensor:
+    """Biased exponent of the smallest power of two >= v, v > 0
+    (test/kernels/deepseek_v41/check_ffn.py:86-89)."""
+    bits = v.float().contiguous().view(torch.int32)
+    return ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) != 0).int()
+
+
+def mxfp8_quant(x: torch.Tensor, rule: str = "aiter"):
+    """Per-32 MXFP8: (e4m3 [.., K], u8 E8M0 codes [.., K/32])
+    (test/kernels/deepseek_v41/check_ffn.py:92-104)."""
+    g = x.float().reshape(*x.shape[:-1], -1, 32)
+    amax = g.abs().amax(-1, keepdim=True)
+    if rule == "aiter":
+        code = code_ceil(amax.clamp_min(1e-10) * (1.0 / 448)).clamp(1, 254)
+    else:
+        code = code_ceil(amax.clamp_min(torch.finfo(torch.float32).tiny) / 448.0).clamp(0, 254)
+    inv = torch.exp2(127.0 - code.float())
+    q = to_e4m3(g * inv).reshape(x.shape)
+    return q, code.squeeze(-1).to(torch.uint8)
+
+
+def mxfp8_dequant(q: torch.Tensor, code: torch.Tensor) -> torch.Tensor:
+    g = q.float().reshape(*q.shape[:-1], -1, 32)
+    return (g * e8m0_value(code).unsqueeze(-1)).reshape(q.shape)
+
+
+def quantize_mxfp4(w: torch.Tensor):
+    """[.., K] f32 -> (packed u8 [.., K/2] low nibble = even k, E8M0 u8 [.., K/32]).
+    Scale: the max's exponent after rounding at mantissa bit 21, less 2; codes: E2M1 RNE
+    saturating at 6 (sgl_amd_mono/muse_spark/mxfp4_quant.py:36-61)."""
+    shape = w.shape
+    xb = w.float().reshape(*shape[:-1], -1, 32)
+    amax = xb.abs().amax(-1, keepdim=True)
+    bits = (amax.contiguous().view(torch.int32) + 0x200000) & -0x800000
+    unb = (((bits >> 23) & 0xFF) - 129).clamp(min=-127)
+    qx = xb * torch.ldexp(torch.ones_like(amax), -unb)
+    a = qx.abs()
+    # RNE onto the E2M1 grid by the decision edges; ties go to the even code
+    edges = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+    code = torch.bucketize(a, edges, right=False)  # a == edge -> lower bucket
+    tie = (a.unsqueeze(-1) == edges).any(-1)
+    code = torch.where(tie & (code % 2 == 1), code + 1, code).clamp(max=7)
+    nib = (code | torch.where(qx < 0, 8, 0)).to(torch.uint8).reshape(*shape[:-1], -1, 2)
+    packed = nib[..., 0] | (nib[..., 1] << 4)
+    return packed, (unb.squeeze(-1) + 127).to(torch.uint8)
+
+
+def dequantize_mxfp4(packed: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """(sgl_amd_mono/muse_spark/mxfp4_quant.py:64-80; sgl_amd_mono/glm53/check.py:438-444)."""
+    codes = torch.stack([packed & 0xF, packed >> 4], -1).reshape(*packed.shape[:-1], -1)
+    mag = torch.tensor(E2M1)[(codes & 7).long()]
+    val = torch.where(codes & 8 != 0, -mag, mag)
+    k = val.shape[-1]
+    return (val.reshape(*packed.shape[:-1], k // 32, 32) * e8m0_value(scales).unsqueeze(-1)).reshape(
+        *packed.shape[:-1], k
+    )

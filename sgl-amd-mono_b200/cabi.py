@@ -1,0 +1,170 @@
+"""ctypes view of the C ABI declared in ``include/b200mono.h``.
+
+The struct layouts are *parsed from the header* rather than restated, so the
+Python side cannot drift from the C side: every ``typedef struct {...} Name;``
+becomes a ``ctypes.Structure`` and every ``int b200mono_*(...)`` prototype an
+attribute of :class:`Lib`.  There is no CPU fallback: if the shared library is
+missing or the device is not sm_100, the calls raise.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+HEADER = os.path.join(os.path.dirname(HERE), "include", "b200mono.h")
+LIB_PATH = os.path.join(HERE, "libb200mono.so")
+
+_SCALARS = {
+    "int32_t": C.c_int32,
+    "uint32_t": C.c_uint32,
+    "int64_t": C.c_int64,
+    "uint64_t": C.c_uint64,
+    "float": C.c_float,
+    "int": C.c_int,
+    "size_t": C.c_size_t,
+}
+
+
+def _strip_comments(text: str) -> str:
+    return re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+
+
+def parse_header(path: str = HEADER):
+    """-> (structs: {name: [(field, ctype)]}, functions: {name: [arg type names]}, enums: {name: int})."""
+    text = _strip_comments(open(path).read())
+    structs: dict[str, list[tuple[str, object]]] = {}
+    for body, name in re.findall(r"typedef\s+struct\s*\{(.*?)\}\s*(\w+)\s*;", text, flags=re.S):
+        fields = []
+        for decl in body.split(";"):
+            decl = " ".join(decl.split())
+            if not decl:
+                continue
+            m = re.match(r"(const\s+)?(\w+)\s*(\*?)\s*(.*)$", decl)
+            base, star, names = m.group(2), m.group(3), m.group(4)
+            for nm in names.split(","):
+                nm = nm.strip()
+                ptr = bool(star) or nm.startswith("*")
+                nm = nm.lstrip("* ")
+                if ptr:
+                    fields.append((nm, C.c_void_p))
+                else:
+                    fields.append((nm, _SCALARS[base]))
+        structs[name] = fields
+    functions = {}
+    for ret, name, args in re.findall(r"\b(int|const char\*)\s+(b200mono_\w+)\s*\(([^)]*)\)\s*;", text):
+        functions[name] = (ret, [a.strip() for a in args.split(",") if a.strip() and a.strip() != "void"])
+    enums = {}
+    for body in re.findall(r"enum\s*\{(.*?)\}", text, flags=re.S):
+        nxt = 0
+        for item in body.split(","):
+            item = item.strip()
+            if not item:
+                continue
+            if "=" in item:
+                k, v = item.split("=")
+                nxt = int(v.strip(), 0)
+                enums[k.strip()] = nxt
+            else:
+                enums[item] = nxt
+            nxt += 1
+    for k, v in re.findall(r"#define\s+(B200MONO_\w+)\s+(-?\d+)", text):
+        enums[k] = int(v)
+    return structs, functions, enums
+
+
+_STRUCT_FIELDS, FUNCTIONS, ENUMS = parse_header()
+
+
+def _make_struct(name: str, fields):
+    return type(name, (C.Structure,), {"_fields_": list(fields)})
+
+
+STRUCTS = {name: _make_struct(name, fields) for name, fields in _STRUCT_FIELDS.items()}
+globals().update(STRUCTS)
+globals().update(ENUMS)
+
+
+class B200MonoError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"b200mono error {code}: {message}")
+        self.code = code
+
+
+def _argtype(decl: str):
+    decl = " ".join(decl.split())
+    if "*" in decl:
+        return C.c_void_p
+    base = decl.replace("const ", "").split(" ")[0]
+    return _SCALARS[base]
+
+
+class Lib:
+    """The loaded shared library.  ``lib.call("moe_ffn", args_struct, stream)`` raises on failure."""
+
+    def __init__(self, path: str = LIB_PATH):
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{path} is missing: build it with `python sgl-amd-mono_b200/build.py` "
+                "(there is no CPU or PyTorch fallback for the kernels)"
+            )
+        self.path = path
+        self.dll = C.CDLL(path)
+        for name, (ret, args) in FUNCTIONS.items():
+            fn = getattr(self.dll, name)
+            fn.restype = C.c_char_p if "char" in ret else C.c_int
+            fn.argtypes = [_argtype(a) for a in args]
+        if self.dll.b200mono_abi_version() != ENUMS["B200MONO_ABI_VERSION"]:
+            raise RuntimeError("libb200mono.so was built from a different header")
+        sizes = (C.c_int32 * 64)()
+        n = self.dll.b200mono_abi_sizes(sizes, 64)
+        mine = [C.sizeof(s) for s in STRUCTS.values()]
+        if list(sizes[:n]) != mine:
+            raise RuntimeError(f"struct layouts differ: library {list(sizes[:n])}, binding {mine}")
+
+    def exports(self):
+        return sorted(FUNCTIONS)
+
+    def last_error(self) -> str:
+        return (self.dll.b200mono_last_error() or b"").decode()
+
+    def call(self, name: str, *args) -> int:
+        fn = getattr(self.dll, "b200mono_" + name)
+        conv = [C.byref(a) if isinstance(a, C.Structure) else a for a in args]
+        rc = fn(*conv)
+        if rc != 0:
+            raise B200MonoError(rc, self.last_error())
+        return rc
+
+    def raw(self, name: str):
+        return getattr(self.dll, "b200mono_" + name)
+
+
+_LIB: Lib | None = None
+
+
+def lib() -> Lib:
+    global _LIB
+    if _LIB is None:
+        _LIB = Lib()
+    return _LIB
+
+
+def ptr(t) -> int | None:
+    """Device address of a torch tensor (None passes NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def fill(struct_name: str, **kw):
+    """Build an args struct; tensors become their data pointers."""
+    s = STRUCTS[struct_name]()
+    known = {f for f, _ in _STRUCT_FIELDS[struct_name]}
+    for k, v in kw.items():
+        if k not in known:
+            raise KeyError(f"{struct_name} has no field {k}")
+        if hasattr(v, "data_ptr"):
+            v = v.data_ptr()
+        setattr(s, k, v)
+    return s

@@ -1,0 +1,277 @@
+// The C ABI: argument validation, scratch layouts and launch sequences.
+// Nothing here allocates or synchronises; every call only enqueues on the
+// caller's stream, so a call is legal inside CUDA-graph capture.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "launch.h"
+
+namespace b200mono {
+
+static thread_local char g_err[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static int cuda_status(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return B200MONO_OK;
+  snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+  return (int)e;
+}
+
+static bool aligned(const void* p, size_t a) { return ((uintptr_t)p % a) == 0; }
+
+#define REQUIRE(cond, ...) \
+  do {                     \
+    if (!(cond)) return fail(B200MONO_E_ARG, __VA_ARGS__); \
+  } while (0)
+
+static int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace b200mono
+
+using namespace b200mono;
+
+extern "C" {
+
+int b200mono_abi_version(void) { return B200MONO_ABI_VERSION; }
+const char* b200mono_last_error(void) { return g_err; }
+
+int b200mono_device_ok(void) {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
+  return major == 10;
+}
+
+int b200mono_abi_sizes(int32_t* out, int32_t capacity) {
+  const int32_t sizes[] = {(int32_t)sizeof(B200NormQuantArgs), (int32_t)sizeof(B200Quant128Args),
+                           (int32_t)sizeof(B200GemvFp8Args),   (int32_t)sizeof(B200RouterArgs),
+                           (int32_t)sizeof(B200MoeUpArgs),     (int32_t)sizeof(B200MoeDownArgs),
+                           (int32_t)sizeof(B200MoeFfnLayout),  (int32_t)sizeof(B200MoeFfnArgs)};
+  const int32_t n = (int32_t)(sizeof(sizes) / sizeof(sizes[0]));
+  for (int32_t i = 0; i < n && i < capacity; ++i) out[i] = sizes[i];
+  return n;
+}
+
+int b200mono_sm_count(void) {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  return n;
+}
+
+int b200mono_norm_quant(const B200NormQuantArgs* a, void* stream) {
+  REQUIRE(a, "norm_quant: null args");
+  REQUIRE(a->x && a->weight && a->q && a->q_scale, "norm_quant: null pointer");
+  REQUIRE(a->rows >= 0 && a->hidden > 0 && a->hidden % 128 == 0 && a->hidden <= 16384,
+          "norm_quant: hidden=%d must be a multiple of 128 and <= 16384", a->hidden);
+  REQUIRE(aligned(a->x, 16) && aligned(a->weight, 16) && aligned(a->q, 8) &&
+              (!a->residual || aligned(a->residual, 16)) && (!a->y || aligned(a->y, 16)) &&
+              (!a->res_out || aligned(a->res_out, 16)),
+          "norm_quant: pointers must be 16-byte aligned");
+  if (a->rows == 0) return B200MONO_OK;
+  return cuda_status(launch_norm_quant(*a, (cudaStream_t)stream), "norm_quant");
+}
+
+int b200mono_quant128(const B200Quant128Args* a, void* stream) {
+  REQUIRE(a, "quant128: null args");
+  REQUIRE(a->x && a->q && a->q_scale, "quant128: null pointer");
+  REQUIRE(a->rows >= 0 && a->cols > 0 && a->cols % 128 == 0, "quant128: cols=%d must be a multiple of 128",
+          a->cols);
+  REQUIRE(aligned(a->x, 16) && aligned(a->q, 8), "quant128: pointers must be 16-byte aligned");
+  return cuda_status(launch_quant128(*a, (cudaStream_t)stream), "quant128");
+}
+
+int b200mono_gemv_fp8(const B200GemvFp8Args* a, void* stream) {
+  REQUIRE(a, "gemv_fp8: null args");
+  REQUIRE(a->w && a->w_scale && a->xq && a->x_scale && a->y, "gemv_fp8: null pointer");
+  REQUIRE(a->rows >= 1 && a->rows <= 32, "gemv_fp8: rows=%d outside 1..32", a->rows);
+  REQUIRE(a->k > 0 && a->k % 128 == 0, "gemv_fp8: k=%d must be a multiple of 128", a->k);
+  REQUIRE(a->groups >= 1 && a->n > 0 && a->n % (16 * a->groups) == 0,
+          "gemv_fp8: n=%d must be a multiple of 16*groups (groups=%d)", a->n, a->groups);
+  REQUIRE(a->groups == 1 || (a->n / a->groups) % 128 == 0 || 128 % (a->n / a->groups) == 0,
+          "gemv_fp8: rows per group must divide or be a multiple of 128");
+  REQUIRE(a->ldy >= a->n, "gemv_fp8: ldy=%d < n=%d", a->ldy, a->n);
+  REQUIRE(aligned(a->w, 32) && aligned(a->xq, 16), "gemv_fp8: w must be 32-byte and xq 16-byte aligned");
+  return cuda_status(launch_gemv_fp8(*a, (cudaStream_t)stream), "gemv_fp8");
+}
+
+int b200mono_router(const B200RouterArgs* a, void* stream) {
+  REQUIRE(a, "router: null args");
+  REQUIRE(a->x && a->gate_w && a->logits && a->topk_ids && a->topk_w && a->union_count &&
+              a->union_ids && a->union_pick && a->counter,
+          "router: null pointer");
+  REQUIRE(a->rows >= 1 && a->rows <= 32, "router: rows=%d outside 1..32", a->rows);
+  REQUIRE(a->hidden > 0 && a->hidden % 8 == 0, "router: hidden=%d must be a multiple of 8", a->hidden);
+  REQUIRE(a->experts >= 1 && a->experts <= 512, "router: experts=%d outside 1..512", a->experts);
+  REQUIRE(a->topk >= 1 && a->topk <= 16 && a->topk <= a->experts, "router: topk=%d outside 1..min(16, experts)",
+          a->topk);
+  REQUIRE(a->score_fn == B200MONO_SCORE_SOFTMAX || a->score_fn == B200MONO_SCORE_SIGMOID_BIAS,
+          "router: score_fn=%d is not built", a->score_fn);
+  REQUIRE(aligned(a->x, 16) && aligned(a->gate_w, 16), "router: x and gate_w must be 16-byte aligned");
+  return cuda_status(launch_router(*a, (cudaStream_t)stream), "router");
+}
+
+static int check_moe_dims(const char* who, int rows, int hidden, int inter, int experts) {
+  REQUIRE(rows >= 1 && rows <= 32, "%s: rows=%d outside 1..32", who, rows);
+  REQUIRE(hidden > 0 && hidden % 128 == 0, "%s: hidden=%d must be a multiple of 128", who, hidden);
+  REQUIRE(inter > 0 && inter % 128 == 0, "%s: inter=%d must be a multiple of 128", who, inter);
+  REQUIRE(experts >= 1 && experts <= 512, "%s: experts=%d outside 1..512", who, experts);
+  return B200MONO_OK;
+}
+
+int b200mono_moe_up(const B200MoeUpArgs* a, void* stream) {
+  REQUIRE(a, "moe_up: null args");
+  REQUIRE(a->xq && a->x_scale && a->w13 && a->w13_scale && a->union_count && a->union_ids && a->mid,
+          "moe_up: null pointer");
+  if (int rc = check_moe_dims("moe_up", a->rows, a->hidden, a->inter, a->experts)) return rc;
+  REQUIRE(a->union_cap >= 1 && a->union_cap <= a->experts + 1, "moe_up: union_cap=%d outside 1..experts+1",
+          a->union_cap);
+  REQUIRE(aligned(a->xq, 16) && aligned(a->w13, 32), "moe_up: w13 must be 32-byte and xq 16-byte aligned");
+  return cuda_status(launch_moe_up(*a, (cudaStream_t)stream), "moe_up");
+}
+
+int b200mono_moe_down(const B200MoeDownArgs* a, void* stream) {
+  REQUIRE(a, "moe_down: null args");
+  REQUIRE(a->midq && a->mid_scale && a->w2 && a->w2_scale && a->union_count && a->union_ids &&
+              a->union_pick && a->topk_w && a->out,
+          "moe_down: null pointer");
+  if (int rc = check_moe_dims("moe_down", a->rows, a->hidden, a->inter, a->experts)) return rc;
+  REQUIRE(a->topk >= 1 && a->topk <= 16, "moe_down: topk=%d outside 1..16", a->topk);
+  REQUIRE(aligned(a->midq, 16) && aligned(a->w2, 32), "moe_down: w2 must be 32-byte and midq 16-byte aligned");
+  return cuda_status(launch_moe_down(*a, (cudaStream_t)stream), "moe_down");
+}
+
+int b200mono_moe_ffn_layout(int32_t rows, int32_t hidden, int32_t inter, int32_t experts, int32_t topk,
+                            B200MoeFfnLayout* out) {
+  REQUIRE(out, "moe_ffn_layout: null out");
+  if (int rc = check_moe_dims("moe_ffn_layout", rows, hidden, inter, experts)) return rc;
+  REQUIRE(topk >= 1 && topk <= 16 && topk <= experts, "moe_ffn_layout: topk=%d outside 1..min(16, experts)", topk);
+  const int cap = union_capacity(rows, topk, experts, 1);
+  int64_t at = 0;
+  auto take = [&](int64_t bytes) {
+    int64_t here = at;
+    at = align_up(at + bytes, 256);
+    return here;
+  };
+  // fixed-position words first: their offsets must not depend on the row count,
+  // because the arrival counter has to stay zero between launches of any width
+  out->counter = take(4);
+  out->union_count = take(4);
+  out->res = take((int64_t)rows * hidden * 2);
+  out->xn = take((int64_t)rows * hidden * 2);
+  out->xq = take((int64_t)rows * hidden);
+  out->xs = take((int64_t)rows * (hidden / 128) * 4);
+  out->logits = take((int64_t)rows * experts * 4);
+  out->topk_ids = take((int64_t)rows * topk * 4);
+  out->topk_w = take((int64_t)rows * topk * 4);
+  out->union_ids = take((int64_t)(experts + 1) * 4);
+  out->union_pick = take((int64_t)(experts + 1) * 32);
+  out->mid = take((int64_t)cap * rows * inter * 2);
+  out->midq = take((int64_t)cap * rows * inter);
+  out->mids = take((int64_t)cap * rows * (inter / 128) * 4);
+  out->total = at;
+  out->union_cap = cap;
+  out->pad_ = 0;
+  return B200MONO_OK;
+}
+
+int b200mono_moe_ffn(const B200MoeFfnArgs* a, void* stream) {
+  REQUIRE(a, "moe_ffn: null args");
+  REQUIRE(a->x && a->out && a->norm_w && a->gate_w && a->w13 && a->w13_scale && a->w2 && a->w2_scale &&
+              a->scratch,
+          "moe_ffn: null pointer");
+  B200MoeFfnLayout L;
+  if (int rc = b200mono_moe_ffn_layout(a->rows, a->hidden, a->inter, a->experts, a->topk, &L)) return rc;
+  if (a->scratch_bytes < L.total)
+    return fail(B200MONO_E_SCRATCH, "moe_ffn: scratch has %lld bytes, needs %lld", (long long)a->scratch_bytes,
+                (long long)L.total);
+  REQUIRE(aligned(a->scratch, 256), "moe_ffn: scratch must be 256-byte aligned");
+  char* sc = (char*)a->scratch;
+  cudaStream_t s = (cudaStream_t)stream;
+
+  B200NormQuantArgs nq{};
+  nq.x = a->x;
+  nq.residual = a->residual;
+  nq.weight = a->norm_w;
+  nq.res_out = sc + L.res;
+  nq.y = sc + L.xn;
+  nq.q = sc + L.xq;
+  nq.q_scale = (float*)(sc + L.xs);
+  nq.rows = a->rows;
+  nq.hidden = a->hidden;
+  nq.eps = a->eps;
+  nq.gemma = 0;
+  if (int rc = b200mono_norm_quant(&nq, s)) return rc;
+
+  B200RouterArgs r{};
+  r.x = sc + L.xn;
+  r.gate_w = a->gate_w;
+  r.bias = a->gate_bias;
+  r.logits = (float*)(sc + L.logits);
+  r.topk_ids = (int32_t*)(sc + L.topk_ids);
+  r.topk_w = (float*)(sc + L.topk_w);
+  r.union_count = (int32_t*)(sc + L.union_count);
+  r.union_ids = (int32_t*)(sc + L.union_ids);
+  r.union_pick = (uint8_t*)(sc + L.union_pick);
+  r.counter = (uint32_t*)(sc + L.counter);
+  r.rows = a->rows;
+  r.hidden = a->hidden;
+  r.experts = a->experts;
+  r.topk = a->topk;
+  r.score_fn = a->score_fn;
+  r.route_scale = a->route_scale;
+  r.has_shared = a->has_shared;
+  if (int rc = b200mono_router(&r, s)) return rc;
+
+  B200MoeUpArgs up{};
+  up.xq = sc + L.xq;
+  up.x_scale = (const float*)(sc + L.xs);
+  up.w13 = a->w13;
+  up.w13_scale = a->w13_scale;
+  up.union_count = r.union_count;
+  up.union_ids = r.union_ids;
+  up.mid = sc + L.mid;
+  up.rows = a->rows;
+  up.hidden = a->hidden;
+  up.inter = a->inter;
+  up.experts = a->experts;
+  up.union_cap = L.union_cap;
+  up.swiglu_limit = a->swiglu_limit;
+  if (int rc = b200mono_moe_up(&up, s)) return rc;
+
+  B200Quant128Args q{};
+  q.x = sc + L.mid;
+  q.q = sc + L.midq;
+  q.q_scale = (float*)(sc + L.mids);
+  q.rows = L.union_cap * a->rows;
+  q.cols = a->inter;
+  q.zero_rule = 0;
+  if (int rc = b200mono_quant128(&q, s)) return rc;
+
+  B200MoeDownArgs dn{};
+  dn.midq = sc + L.midq;
+  dn.mid_scale = (const float*)(sc + L.mids);
+  dn.w2 = a->w2;
+  dn.w2_scale = a->w2_scale;
+  dn.union_count = r.union_count;
+  dn.union_ids = r.union_ids;
+  dn.union_pick = r.union_pick;
+  dn.topk_w = r.topk_w;
+  dn.residual = a->add_residual ? (a->residual ? (const void*)(sc + L.res) : a->x) : nullptr;
+  dn.out = a->out;
+  dn.rows = a->rows;
+  dn.hidden = a->hidden;
+  dn.inter = a->inter;
+  dn.experts = a->experts;
+  dn.topk = a->topk;
+  return b200mono_moe_down(&dn, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,192 @@
+// Device-side building blocks shared by every decode-monokernel stage (sm_100a only).
+//
+// Contents: packed bf16 / e4m3 conversions, cache-hinted 128-bit loads, the
+// m16n8k32 e4m3 tensor-core primitive used by the swap-AB weight-streaming
+// GEMVs, warp reductions with a fixed order, and "defined" transcendental
+// functions (det_*) whose every f32 operation is spelled out so that a CPU
+// restatement using IEEE f32 arithmetic reproduces them bit for bit.  The
+// routing decisions (router top-k, index top-k) depend on those bits.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+#ifndef __CUDA_ARCH__
+#define B200_DEVICE_ONLY
+#endif
+
+namespace b200mono {
+
+constexpr int kWarp = 32;
+constexpr float kFp8Max = 448.0f;
+
+// ---------------------------------------------------------------- bf16 helpers
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) {
+  return __uint_as_float(bits16 << 16);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t pair) { return __uint_as_float(pair << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t pair) { return __uint_as_float(pair & 0xffff0000u); }
+// round-to-nearest-even f32 -> bf16 bits (NaN kept quiet), the same rule as torch's .to(bfloat16)
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float f) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ float round_bf16(float f) {
+  return __bfloat162float(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
+}
+
+// ---------------------------------------------------------------- e4m3 helpers
+// RNE, saturating to +-448 (never NaN for finite input).
+__device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float a, float b, float c, float d) {
+  uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint32_t two) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(two & 0xffffu), __NV_E4M3);
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+__device__ __forceinline__ float e4m3_to_f32(uint32_t one) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(one & 0xffu), __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// ---------------------------------------------------------------- loads
+// Weights are read exactly once per launch: keep them out of L1 and mark them
+// first to leave L2, so KV pages, activations and scratch stay resident.
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// sm_100 has 256-bit global loads: one lane fetches a whole 32-byte sector, four
+// lanes a whole 128-byte line.  `p` must be 32-byte aligned.
+struct __align__(32) U256 {
+  uint32_t v[8];
+};
+__device__ __forceinline__ U256 ld_stream_u256(const void* p) {
+  U256 r;
+  asm volatile(
+      "ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]),
+        "=r"(r.v[6]), "=r"(r.v[7])
+      : "l"(p));
+  return r;
+}
+// Activations produced by an earlier launch: ordinary cached load.
+__device__ __forceinline__ uint4 ld_u4(const void* p) {
+  return *reinterpret_cast<const uint4*>(p);
+}
+// Values produced by another CTA of the same launch or by a peer GPU: L2 / system coherent.
+__device__ __forceinline__ uint32_t ld_relaxed_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_sys_u4(void* p, uint4 v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// ---------------------------------------------------------------- tensor core
+// D(16x8,f32) += A(16x32,e4m3,row) * B(32x8,e4m3,col).  lane = 4*g + c:
+//   a0: row g   k-slots 4c..4c+3      a1: row g+8 k-slots 4c..4c+3
+//   a2: row g   k-slots 16+4c..       a3: row g+8 k-slots 16+4c..
+//   b0: col g   k-slots 4c..4c+3      b1: col g   k-slots 16+4c..
+//   d0: (g,2c) d1: (g,2c+1) d2: (g+8,2c) d3: (g+8,2c+1)
+// A dot product does not care which k sits in which slot as long as A and B
+// agree, so both sides load 32 contiguous bytes at k0+32c (one 128-k block is
+// four lanes wide) and feed words {2m, 2m+1} to MMA m = 0..3: no shuffle, no
+// shared-memory stage.
+__device__ __forceinline__ void mma_e4m3_16x8x32(float (&d)[4], uint32_t a0, uint32_t a1,
+                                                 uint32_t a2, uint32_t a3, uint32_t b0,
+                                                 uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------- reductions
+// xor tree 16,8,4,2,1: every lane ends with the same bits (f32 add commutes).
+__device__ __forceinline__ float warp_sum_tree(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    unsigned long long o = __shfl_xor_sync(0xffffffffu, v, off);
+    v = o > v ? o : v;
+  }
+  return v;
+}
+
+// ---------------------------------------------------------------- defined math
+// exp(x): n = rint(x*log2e); r = x - n*ln2_hi - n*ln2_lo; degree-6 Horner in
+// separately rounded mul/add; result scaled by 2^n through the exponent bits.
+// Max error about 2 ulp on [-87, 88]; what matters is that it is *defined*.
+__device__ __forceinline__ float det_exp(float x) {
+  x = fminf(fmaxf(x, -87.0f), 88.0f);
+  float n = rintf(__fmul_rn(x, 1.4426950408889634f));
+  float r = __fsub_rn(x, __fmul_rn(n, 0.693145751953125f));
+  r = __fsub_rn(r, __fmul_rn(n, 1.428606765330187e-06f));
+  float p = 1.3888889225e-03f;                              // 1/720
+  p = __fadd_rn(__fmul_rn(p, r), 8.3333337680e-03f);        // 1/120
+  p = __fadd_rn(__fmul_rn(p, r), 4.1666667908e-02f);        // 1/24
+  p = __fadd_rn(__fmul_rn(p, r), 1.6666667163e-01f);        // 1/6
+  p = __fadd_rn(__fmul_rn(p, r), 0.5f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+  int e = (int)n;  // in [-126, 127]
+  // two-step scaling keeps 2^e representable at both ends
+  int e1 = e / 2, e2 = e - e1;
+  float s1 = __int_as_float((e1 + 127) << 23), s2 = __int_as_float((e2 + 127) << 23);
+  return __fmul_rn(__fmul_rn(p, s1), s2);
+}
+__device__ __forceinline__ float det_sigmoid(float x) {
+  return __fdiv_rn(1.0f, __fadd_rn(1.0f, det_exp(-x)));
+}
+// x * sigmoid(x)
+__device__ __forceinline__ float det_silu(float x) { return __fmul_rn(x, det_sigmoid(x)); }
+__device__ __forceinline__ float det_rsqrt(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
+
+// Order-preserving u32 image of f32 bits: larger float <=> larger key.
+__device__ __forceinline__ uint32_t radix_key(float f) {
+  uint32_t b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b ^ 0x80000000u);
+}
+
+}  // namespace b200mono

@@ -1,0 +1,269 @@
+// Kernels built on the weight-streaming core: the generic (optionally
+// block-diagonal) block-FP8 GEMV, the routed/shared expert gate-up GEMV with
+// SwiGLU, and the expert down GEMV with the slot-ordered bf16 combine.
+#include "gemv.cuh"
+#include "launch.h"
+
+namespace b200mono {
+
+struct GemvP {
+  const uint8_t* w;
+  const float* ws;
+  const uint8_t* x;
+  const float* xs;
+  void* y;
+  int rows, n, k, groups, ldy, y_f32;
+  int ks;      // k slices per CTA (1, 2, 4, 8); 8/ks row tiles per CTA
+  int rowset;  // R == 2: rows between the gate and the up row of one output column
+  int ntiles;  // 16-row tiles per matrix (per expert)
+  // expert indirection (MoE up): blockIdx.y = union entry
+  const int* union_count;
+  const int* union_ids;
+  long long w_stride_e, ws_stride_e, y_stride_u;
+  float limit;
+};
+
+// R == 1: y[t, n] plain store.  R == 2: SwiGLU of (gate row n, up row n + rowset).
+template <int R, int NT>
+__global__ __launch_bounds__(256) void gemv_kernel(GemvP p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int rtw = 8 / p.ks;
+  const int rt_local = warp / p.ks, ksl = warp % p.ks;
+  const uint8_t* w = p.w;
+  const float* wscale = p.ws;
+  char* y = reinterpret_cast<char*>(p.y);
+  if (p.union_count) {
+    const int u = blockIdx.y;
+    if (u >= *p.union_count) return;
+    const int e = p.union_ids[u];
+    w += (long long)e * p.w_stride_e;
+    wscale += (long long)e * p.ws_stride_e;
+    y += (long long)u * p.y_stride_u;
+  }
+  const int rt = blockIdx.x * rtw + rt_local;
+  const bool active = rt < p.ntiles;
+  const int n0 = rt * 16;
+  const int KB = p.k >> 7;
+  float acc[R][NT][4];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[r][nt][i] = 0.f;
+
+  if (active) {
+    const int group = n0 / (p.n / p.groups);
+    const size_t ldx = (size_t)p.groups * p.k;
+    const size_t ldxs = (size_t)p.groups * KB;
+    XView<NT> xv = make_xview<NT>(p.x + (size_t)group * p.k, ldx, p.xs + (size_t)group * KB, ldxs,
+                                  p.rows, lane);
+    const uint8_t* wp[R];
+    const float* wsc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int row0 = n0 + r * p.rowset;
+      wp[r] = w + (size_t)(row0 + g) * p.k + 32 * c;
+      wsc[r] = wscale + (size_t)(row0 >> 7) * KB;
+    }
+    const int kb0 = (int)((long long)ksl * KB / p.ks), kb1 = (int)((long long)(ksl + 1) * KB / p.ks);
+    stream_tile<R, NT, false>(wp, (size_t)p.k, wsc, xv, kb0, kb1, acc);
+  }
+
+  __shared__ float red[8][R * NT * 4][32];
+  if (p.ks > 1) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[warp][(r * NT + nt) * 4 + i][lane] = acc[r][nt][i];
+    __syncthreads();
+    if (ksl != 0 || !active) return;
+    // slice order 0, 1, ..: the sum is the same on every launch
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float v = acc[r][nt][i];
+          for (int s = 1; s < p.ks; ++s) v += red[warp + s][(r * NT + nt) * 4 + i][lane];
+          acc[r][nt][i] = v;
+        }
+  } else if (!active) {
+    return;
+  }
+
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = nt * 8 + 2 * c + (i & 1);
+      const int row = n0 + g + ((i & 2) ? 8 : 0);
+      if (t >= p.rows) continue;
+      if (R == 1) {
+        if (p.y_f32)
+          reinterpret_cast<float*>(y)[(size_t)t * p.ldy + row] = acc[0][nt][i];
+        else
+          reinterpret_cast<__nv_bfloat16*>(y)[(size_t)t * p.ldy + row] =
+              __float2bfloat16_rn(acc[0][nt][i]);
+      } else {
+        float gate = acc[0][nt][i], up = acc[R - 1][nt][i];
+        if (p.limit > 0.f) {
+          gate = fminf(gate, p.limit);
+          up = fminf(fmaxf(up, -p.limit), p.limit);
+        }
+        reinterpret_cast<__nv_bfloat16*>(y)[(size_t)t * p.ldy + row] =
+            __float2bfloat16_rn(det_silu(gate) * up);
+      }
+    }
+}
+
+static int pick_ks(int KB) {
+  int ks = 1;
+  while (ks * 2 <= 8 && ks * 2 <= KB) ks *= 2;
+  return ks;
+}
+
+template <int R>
+static cudaError_t launch_gemv_r(const GemvP& p, dim3 grid, cudaStream_t s) {
+  if (p.rows <= 8)
+    gemv_kernel<R, 1><<<grid, 256, 0, s>>>(p);
+  else if (p.rows <= 16)
+    gemv_kernel<R, 2><<<grid, 256, 0, s>>>(p);
+  else
+    gemv_kernel<R, 4><<<grid, 256, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gemv_fp8(const B200GemvFp8Args& a, cudaStream_t s) {
+  GemvP p{};
+  p.w = (const uint8_t*)a.w;
+  p.ws = a.w_scale;
+  p.x = (const uint8_t*)a.xq;
+  p.xs = a.x_scale;
+  p.y = a.y;
+  p.rows = a.rows;
+  p.n = a.n;
+  p.k = a.k;
+  p.groups = a.groups;
+  p.ldy = a.ldy;
+  p.y_f32 = a.y_f32;
+  p.ks = pick_ks(a.k >> 7);
+  p.rowset = 0;
+  p.ntiles = a.n / 16;
+  const int rtw = 8 / p.ks;
+  dim3 grid((p.ntiles + rtw - 1) / rtw, 1);
+  return launch_gemv_r<1>(p, grid, s);
+}
+
+cudaError_t launch_moe_up(const B200MoeUpArgs& a, cudaStream_t s) {
+  GemvP p{};
+  p.w = (const uint8_t*)a.w13;
+  p.ws = a.w13_scale;
+  p.x = (const uint8_t*)a.xq;
+  p.xs = a.x_scale;
+  p.y = a.mid;
+  p.rows = a.rows;
+  p.n = a.inter;  // one group: the whole matrix
+  p.k = a.hidden;
+  p.groups = 1;
+  p.ldy = a.inter;
+  p.y_f32 = 0;
+  p.ks = pick_ks(a.hidden >> 7);
+  p.rowset = a.inter;
+  p.ntiles = a.inter / 16;
+  p.union_count = a.union_count;
+  p.union_ids = a.union_ids;
+  p.w_stride_e = 2ll * a.inter * a.hidden;
+  p.ws_stride_e = (long long)((2 * a.inter + 127) / 128) * (a.hidden / 128);
+  p.y_stride_u = (long long)a.rows * a.inter * 2;
+  p.limit = a.swiglu_limit;
+  const int rtw = 8 / p.ks;
+  // the union size lives on the device: launch for the largest possible union
+  const int cap = a.union_cap;
+  dim3 grid((p.ntiles + rtw - 1) / rtw, cap);
+  return launch_gemv_r<2>(p, grid, s);
+}
+
+// ------------------------------------------------------------------ expert down + combine
+// Task = RB (8 or 16) rows of the hidden dimension.  The 8 warps of a CTA take
+// the union entries round-robin; each computes y = W2[e][rows] . midq[u] for all
+// activation rows and files bf16(y * w) under the slot that picked the expert.
+// The combine then walks the slots in order with a bf16 rounding at each add.
+template <int NT, bool HALF>
+__global__ __launch_bounds__(256) void moe_down_kernel(B200MoeDownArgs a) {
+  extern __shared__ float contrib[];  // [topk+1][rows][RB]
+  constexpr int RB = HALF ? 8 : 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int n0 = blockIdx.x * RB;
+  const int U = *a.union_count;
+  const int KB = a.inter >> 7;
+  const int T = a.rows;
+  for (int u = warp; u < U; u += 8) {
+    const int e = a.union_ids[u];
+    const uint8_t* w = (const uint8_t*)a.w2 + (size_t)e * a.hidden * a.inter;
+    const float* ws = a.w2_scale + (size_t)e * ((a.hidden + 127) / 128) * KB;
+    XView<NT> xv = make_xview<NT>((const uint8_t*)a.midq + (size_t)u * T * a.inter, (size_t)a.inter,
+                                  a.mid_scale + (size_t)u * T * KB, (size_t)KB, T, lane);
+    const uint8_t* wp[1] = {w + (size_t)(n0 + g) * a.inter + 32 * c};
+    const float* wsc[1] = {ws + (size_t)(n0 >> 7) * KB};
+    float acc[1][NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[0][nt][i] = 0.f;
+    stream_tile<1, NT, HALF>(wp, (size_t)a.inter, wsc, xv, 0, KB, acc);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = nt * 8 + 2 * c + (i & 1);
+        const int rl = g + ((i & 2) ? 8 : 0);
+        if (t >= T || rl >= RB) continue;
+        const int slot = a.union_pick[u * 32 + t];
+        if (!slot) continue;
+        const float wgt = slot <= a.topk ? a.topk_w[(size_t)t * a.topk + slot - 1] : 1.0f;
+        contrib[((slot - 1) * T + t) * RB + rl] = round_bf16(__fmul_rn(acc[0][nt][i], wgt));
+      }
+  }
+  __syncthreads();
+  const int slots = a.topk + 1;
+  for (int i = threadIdx.x; i < T * RB; i += 256) {
+    const int t = i / RB, rl = i % RB;
+    float sum = 0.f;
+    for (int sl = 0; sl < slots; ++sl) {
+      // a slot nobody filled (no shared expert) contributes nothing
+      const bool filled = sl < a.topk || a.union_ids[U - 1] == a.experts;
+      if (filled) sum = round_bf16(__fadd_rn(sum, contrib[(sl * T + t) * RB + rl]));
+    }
+    if (a.residual)
+      sum = round_bf16(__fadd_rn(
+          sum, __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.residual)[(size_t)t * a.hidden + n0 + rl])));
+    reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)t * a.hidden + n0 + rl] = __float2bfloat16_rn(sum);
+  }
+}
+
+template <bool HALF>
+static cudaError_t launch_down_h(const B200MoeDownArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
+  if (a.rows <= 8)
+    moe_down_kernel<1, HALF><<<grid, 256, smem, s>>>(a);
+  else if (a.rows <= 16)
+    moe_down_kernel<2, HALF><<<grid, 256, smem, s>>>(a);
+  else
+    moe_down_kernel<4, HALF><<<grid, 256, smem, s>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_moe_down(const B200MoeDownArgs& a, cudaStream_t s) {
+  // 8-row tasks when 16-row tasks would leave SMs without work
+  int sms = 148;
+  const bool half = a.hidden / 16 < 2 * sms;
+  const int rb = half ? 8 : 16;
+  const size_t smem = (size_t)(a.topk + 1) * a.rows * rb * sizeof(float);
+  dim3 grid(a.hidden / rb);
+  return half ? launch_down_h<true>(a, grid, smem, s) : launch_down_h<false>(a, grid, smem, s);
+}
+
+}  // namespace b200mono

@@ -1,0 +1,25 @@
+// Internal host-side launch interface between the C ABI (api.cu) and the
+// kernel translation units.  Every function enqueues on `stream` and returns
+// the cudaError_t of the launch; argument validation happens in api.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200mono.h"
+
+namespace b200mono {
+
+cudaError_t launch_norm_quant(const B200NormQuantArgs& a, cudaStream_t s);
+cudaError_t launch_quant128(const B200Quant128Args& a, cudaStream_t s);
+cudaError_t launch_router(const B200RouterArgs& a, cudaStream_t s);
+cudaError_t launch_gemv_fp8(const B200GemvFp8Args& a, cudaStream_t s);
+cudaError_t launch_moe_up(const B200MoeUpArgs& a, cudaStream_t s);
+cudaError_t launch_moe_down(const B200MoeDownArgs& a, cudaStream_t s);
+
+// upper bound of distinct experts a step can pick (+1 shared)
+inline int union_capacity(int rows, int topk, int experts, int has_shared) {
+  int u = rows * topk < experts ? rows * topk : experts;
+  return u + (has_shared ? 1 : 0);
+}
+
+}  // namespace b200mono

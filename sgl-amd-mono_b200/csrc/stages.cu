@@ -1,0 +1,344 @@
+// Row-wise stages of the decode layer: (residual add +) RMSNorm + per-128 FP8
+// activation quant, plain per-128 quant, and the router (gate GEMV in a fixed
+// summation order, score, exact top-k, union of picked experts).
+//
+// The arithmetic of every f32 value that can change a routing decision is
+// written with explicitly rounded operations (__fadd_rn, __fmul_rn, ...) in a
+// stated order, so the compiler cannot contract or reassociate them and a CPU
+// restatement reproduces the bits.
+#include "common.cuh"
+#include "launch.h"
+
+namespace b200mono {
+
+// ------------------------------------------------------------------ norm + quant
+// One CTA of 256 threads per row.  Thread i owns the 8-column vectors
+// i, i+256, ...; its sum of squares runs over them in order (element 0..7
+// inside a vector), lane sums meet in an xor tree, warp sums are added in warp
+// order.  A 128-column quant group is 16 consecutive vectors = 16 consecutive
+// lanes of one warp.
+template <bool HAS_RES>
+__global__ __launch_bounds__(256) void norm_quant_kernel(B200NormQuantArgs a) {
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nvec = a.hidden >> 3;
+  const uint4* x = reinterpret_cast<const uint4*>(a.x) + (size_t)row * nvec;
+  const uint4* r = HAS_RES ? reinterpret_cast<const uint4*>(a.residual) + (size_t)row * nvec : nullptr;
+  const uint4* w = reinterpret_cast<const uint4*>(a.weight);
+  __shared__ float warp_part[8];
+
+  auto load_s = [&](int v, float (&s)[8]) {
+    uint4 xv = x[v];
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      s[2 * j] = bf16_lo(xw[j]);
+      s[2 * j + 1] = bf16_hi(xw[j]);
+    }
+    if (HAS_RES) {
+      uint4 rv = r[v];
+      const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        s[2 * j] = __fadd_rn(s[2 * j], bf16_lo(rw[j]));
+        s[2 * j + 1] = __fadd_rn(s[2 * j + 1], bf16_hi(rw[j]));
+      }
+    }
+  };
+
+  float ss = 0.f;
+  for (int v = tid; v < nvec; v += 256) {
+    float s[8];
+    load_s(v, s);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(s[j], s[j]));
+  }
+  ss = warp_sum_tree(ss);
+  if (lane == 0) warp_part[warp] = ss;
+  __syncthreads();
+  float tot = warp_part[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) tot = __fadd_rn(tot, warp_part[i]);
+  const float var = __fdiv_rn(tot, (float)a.hidden);
+  const float rstd = det_rsqrt(__fadd_rn(var, a.eps));
+
+  for (int v0 = warp * 32; v0 < nvec; v0 += 256) {
+    const int v = v0 + lane;
+    const bool ok = v < nvec;
+    float y[8];
+    float amax = 0.f;
+    if (ok) {
+      float s[8];
+      load_s(v, s);
+      uint4 wv = w[v];
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t res_bits[4], y_bits[4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float wf = (j & 1) ? bf16_hi(ww[j >> 1]) : bf16_lo(ww[j >> 1]);
+        if (a.gemma) wf = __fadd_rn(1.0f, wf);
+        y[j] = round_bf16(__fmul_rn(__fmul_rn(s[j], rstd), wf));
+        amax = fmaxf(amax, fabsf(y[j]));
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        y_bits[j] = pack_bf16x2(y[2 * j], y[2 * j + 1]);
+        res_bits[j] = pack_bf16x2(s[2 * j], s[2 * j + 1]);
+      }
+      if (a.y)
+        reinterpret_cast<uint4*>(a.y)[(size_t)row * nvec + v] =
+            make_uint4(y_bits[0], y_bits[1], y_bits[2], y_bits[3]);
+      if (HAS_RES && a.res_out)
+        reinterpret_cast<uint4*>(a.res_out)[(size_t)row * nvec + v] =
+            make_uint4(res_bits[0], res_bits[1], res_bits[2], res_bits[3]);
+    }
+    // amax over the 16 lanes that share a 128-column group
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (ok) {
+      const float scale = __fdiv_rn(fmaxf(amax, 1e-10f), kFp8Max);
+      float q[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = fminf(fmaxf(__fdiv_rn(y[j], scale), -kFp8Max), kFp8Max);
+      uint2 packed;
+      packed.x = f32x4_to_e4m3x4(q[0], q[1], q[2], q[3]);
+      packed.y = f32x4_to_e4m3x4(q[4], q[5], q[6], q[7]);
+      reinterpret_cast<uint2*>(a.q)[(size_t)row * nvec + v] = packed;
+      if ((lane & 15) == 0) a.q_scale[(size_t)row * (a.hidden >> 7) + (v >> 4)] = scale;
+    }
+  }
+}
+
+cudaError_t launch_norm_quant(const B200NormQuantArgs& a, cudaStream_t s) {
+  if (a.residual)
+    norm_quant_kernel<true><<<a.rows, 256, 0, s>>>(a);
+  else
+    norm_quant_kernel<false><<<a.rows, 256, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ plain per-128 quant
+__global__ __launch_bounds__(256) void quant128_kernel(B200Quant128Args a) {
+  const long long total = (long long)a.rows * (a.cols >> 3);
+  const long long v = (long long)blockIdx.x * 256 + threadIdx.x;
+  const bool ok = v < total;
+  float y[8];
+  float amax = 0.f;
+  if (ok) {
+    uint4 xv = reinterpret_cast<const uint4*>(a.x)[v];
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      y[2 * j] = bf16_lo(xw[j]);
+      y[2 * j + 1] = bf16_hi(xw[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
+  }
+#pragma unroll
+  for (int off = 8; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if (ok) {
+    float scale;
+    if (a.zero_rule)
+      scale = amax > 0.f ? __fdiv_rn(amax, kFp8Max) : 1.0f;
+    else
+      scale = __fdiv_rn(fmaxf(amax, 1e-10f), kFp8Max);
+    float q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = fminf(fmaxf(__fdiv_rn(y[j], scale), -kFp8Max), kFp8Max);
+    uint2 packed;
+    packed.x = f32x4_to_e4m3x4(q[0], q[1], q[2], q[3]);
+    packed.y = f32x4_to_e4m3x4(q[4], q[5], q[6], q[7]);
+    reinterpret_cast<uint2*>(a.q)[v] = packed;
+    if ((threadIdx.x & 15) == 0) a.q_scale[v >> 4] = scale;
+  }
+}
+
+cudaError_t launch_quant128(const B200Quant128Args& a, cudaStream_t s) {
+  const long long total = (long long)a.rows * (a.cols >> 3);
+  if (total == 0) return cudaSuccess;
+  quant128_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ router
+// Phase 1 (all CTAs): warp per expert, logits for every row in the stated order.
+// Phase 2 (the CTA that arrives last): warp per row, score + exact top-k by
+// (key descending, expert id ascending) + weights; then the union of picked
+// experts in ascending id order and, per union entry, which slot of which row
+// picked it.
+constexpr int kMaxExperts = 512;
+
+template <int MAXT>
+__global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int T = a.rows, E = a.experts, H = a.hidden;
+  {
+    const int e = blockIdx.x * 8 + warp;
+    if (e < E) {
+      float acc[MAXT];
+#pragma unroll
+      for (int t = 0; t < MAXT; ++t) acc[t] = 0.f;
+      const uint4* wrow = reinterpret_cast<const uint4*>(a.gate_w) + (size_t)e * (H >> 3);
+      const uint4* xb = reinterpret_cast<const uint4*>(a.x);
+      for (int v = lane; v < (H >> 3); v += 32) {
+        uint4 wv = ld_stream_u4(wrow + v);
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int t = 0; t < MAXT; ++t) {
+          if (t < T) {
+            uint4 xv = xb[(size_t)t * (H >> 3) + v];
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              // bf16 x bf16 is exact in f32, so each step is one rounding
+              acc[t] = __fadd_rn(acc[t], __fmul_rn(bf16_lo(xw[j]), bf16_lo(ww[j])));
+              acc[t] = __fadd_rn(acc[t], __fmul_rn(bf16_hi(xw[j]), bf16_hi(ww[j])));
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < MAXT; ++t) {
+        if (t < T) {
+          float v = warp_sum_tree(acc[t]);
+          if (lane == 0) a.logits[(size_t)t * E + e] = v;
+        }
+      }
+    }
+  }
+  // ---- last CTA does the selection
+  __shared__ int s_last;
+  __shared__ int s_ids[32 * 16];
+  __shared__ unsigned char s_flag[kMaxExperts];
+  __shared__ short s_slot[kMaxExperts];
+  __shared__ int s_count;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned old = atomicAdd(a.counter, 1u);
+    s_last = (old == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int e = tid; e < E; e += 256) s_flag[e] = 0;
+  __syncthreads();
+
+  const int K = a.topk;
+  for (int t = warp; t < T; t += 8) {
+    // lane owns experts lane, lane+32, ...
+    float score[kMaxExperts / 32];
+    uint32_t key[kMaxExperts / 32];
+    unsigned taken = 0;
+#pragma unroll
+    for (int j = 0; j < kMaxExperts / 32; ++j) {
+      const int e = lane + 32 * j;
+      score[j] = 0.f;
+      key[j] = 0;
+      if (e < E) {
+        float l = __ldcg(a.logits + (size_t)t * E + e);
+        if (a.score_fn == B200MONO_SCORE_SOFTMAX) {
+          score[j] = l;
+          key[j] = radix_key(l);
+        } else {
+          float sg = det_sigmoid(l);
+          score[j] = sg;
+          key[j] = radix_key(a.bias ? __fadd_rn(sg, a.bias[e]) : sg);
+        }
+      } else {
+        taken |= 1u << j;
+      }
+    }
+    float my_raw = 0.f;  // lane kk keeps the raw score of rank kk
+    int my_id = 0;
+    for (int kk = 0; kk < K; ++kk) {
+      unsigned long long best = 0;
+#pragma unroll
+      for (int j = 0; j < kMaxExperts / 32; ++j) {
+        if (!(taken & (1u << j))) {
+          unsigned long long cand =
+              ((unsigned long long)key[j] << 32) | (uint32_t)(0xffffffffu - (uint32_t)(lane + 32 * j));
+          best = cand > best ? cand : best;
+        }
+      }
+      const unsigned long long win = warp_max_u64(best);
+      const int e = (int)(0xffffffffu - (uint32_t)(win & 0xffffffffu));
+      float raw = 0.f;
+#pragma unroll
+      for (int j = 0; j < kMaxExperts / 32; ++j)
+        if (lane + 32 * j == e) {
+          taken |= 1u << j;
+          raw = score[j];
+        }
+      raw = __shfl_sync(0xffffffffu, raw, e & 31);
+      if (lane == kk) {
+        my_raw = raw;
+        my_id = e;
+      }
+    }
+    // weights
+    float wgt;
+    if (a.score_fn == B200MONO_SCORE_SOFTMAX) {
+      const float top = __shfl_sync(0xffffffffu, my_raw, 0);
+      wgt = lane < K ? det_exp(__fsub_rn(my_raw, top)) : 0.f;
+    } else {
+      wgt = lane < K ? my_raw : 0.f;
+    }
+    float sum = 0.f;
+    for (int kk = 0; kk < K; ++kk) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, wgt, kk));
+    wgt = __fdiv_rn(wgt, sum);
+    if (a.score_fn != B200MONO_SCORE_SOFTMAX) wgt = __fmul_rn(wgt, a.route_scale);
+    if (lane < K) {
+      a.topk_ids[(size_t)t * K + lane] = my_id;
+      a.topk_w[(size_t)t * K + lane] = wgt;
+      s_ids[t * 16 + lane] = my_id;
+      s_flag[my_id] = 1;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int base = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const bool f = e < E && s_flag[e];
+      const unsigned m = __ballot_sync(0xffffffffu, f);
+      if (f) {
+        const int pos = base + __popc(m & ((1u << lane) - 1u));
+        a.union_ids[pos] = e;
+        s_slot[e] = (short)pos;
+      }
+      base += __popc(m);
+    }
+    if (lane == 0) s_count = base;
+  }
+  __syncthreads();
+  const int U = s_count;
+  const int UT = U + (a.has_shared ? 1 : 0);
+  for (int i = tid; i < UT * 32; i += 256) a.union_pick[i] = 0;
+  __syncthreads();
+  for (int i = tid; i < T * K; i += 256) {
+    const int t = i / K, kk = i % K;
+    a.union_pick[s_slot[s_ids[t * 16 + kk]] * 32 + t] = (unsigned char)(kk + 1);
+  }
+  if (a.has_shared) {
+    if (tid < T) a.union_pick[U * 32 + tid] = (unsigned char)(K + 1);
+    if (tid == 0) a.union_ids[U] = E;
+  }
+  if (tid == 0) {
+    *a.union_count = UT;
+    *a.counter = 0;
+  }
+}
+
+cudaError_t launch_router(const B200RouterArgs& a, cudaStream_t s) {
+  const unsigned grid = (unsigned)((a.experts + 7) / 8);
+  if (a.rows <= 8)
+    router_kernel<8><<<grid, 256, 0, s>>>(a);
+  else if (a.rows <= 16)
+    router_kernel<16><<<grid, 256, 0, s>>>(a);
+  else
+    router_kernel<32><<<grid, 256, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace b200mono

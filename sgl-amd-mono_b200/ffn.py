@@ -1,0 +1,109 @@
+"""Host runner of the MoE FFN launch: validates tensors, owns the scratch, passes raw
+device addresses and ints to the C ABI on the current stream.
+
+Mirrors the reference runner's ``ffn`` entry
+(sgl_amd_mono/deepseek_v41/gfx950/runner.py:266-856: buffers and scratch owned by the
+runner, shapes and dtypes checked on the host, nothing allocated per step).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from . import cabi
+
+
+@dataclasses.dataclass(frozen=True)
+class FfnBuild:
+    """Build key of one FFN variant (cf. MonoBuild, sgl_amd_mono/deepseek_v41/gfx950/layer.py:80-105)."""
+
+    width: int  # activation rows the buffers are sized for (1..32)
+    hidden: int
+    inter: int  # this rank's slice of the expert intermediate size
+    experts: int
+    topk: int
+    score_fn: int = 0
+    has_shared: bool = True
+    route_scale: float = 1.0
+    eps: float = 1e-6
+    swiglu_limit: float = 0.0
+
+
+@dataclasses.dataclass
+class FfnWeights:
+    """Device tensors in checkpoint layout; the shared expert is the last expert entry."""
+
+    norm: torch.Tensor  # bf16 [hidden]
+    gate_w: torch.Tensor  # bf16 [experts, hidden]
+    bias: torch.Tensor | None  # f32 [experts]
+    w13: torch.Tensor  # e4m3 [experts(+1), 2*inter, hidden]
+    w13_s: torch.Tensor  # f32 [experts(+1), 2*inter/128, hidden/128]
+    w2: torch.Tensor  # e4m3 [experts(+1), hidden, inter]
+    w2_s: torch.Tensor  # f32 [experts(+1), hidden/128, inter/128]
+
+
+def _check(t: torch.Tensor, name: str, dtype, shape):
+    if t.dtype != dtype or tuple(t.shape) != tuple(shape) or not t.is_contiguous() or not t.is_cuda:
+        raise ValueError(
+            f"{name}: expected contiguous cuda {dtype} {tuple(shape)}, got {t.dtype} {tuple(t.shape)} on {t.device}"
+        )
+
+
+class FfnRunner:
+    def __init__(self, build: FfnBuild, weights: FfnWeights, device: torch.device | str = "cuda"):
+        self.lib = cabi.lib()
+        self.build, self.w = build, weights
+        self.device = torch.device(device)
+        with torch.cuda.device(self.device):
+            if not self.lib.dll.b200mono_device_ok():
+                raise RuntimeError("b200mono needs an sm_100 device")
+        b = build
+        n = b.experts + (1 if b.has_shared else 0)
+        _check(weights.norm, "norm", torch.bfloat16, (b.hidden,))
+        _check(weights.gate_w, "gate_w", torch.bfloat16, (b.experts, b.hidden))
+        if weights.bias is not None:
+            _check(weights.bias, "bias", torch.float32, (b.experts,))
+        _check(weights.w13, "w13", torch.float8_e4m3fn, (n, 2 * b.inter, b.hidden))
+        _check(weights.w13_s, "w13_s", torch.float32, (n, -(-2 * b.inter // 128), b.hidden // 128))
+        _check(weights.w2, "w2", torch.float8_e4m3fn, (n, b.hidden, b.inter))
+        _check(weights.w2_s, "w2_s", torch.float32, (n, b.hidden // 128, b.inter // 128))
+        self.layout = cabi.STRUCTS["B200MoeFfnLayout"]()
+        self.lib.call("moe_ffn_layout", b.width, b.hidden, b.inter, b.experts, b.topk, self.layout)
+        # zeroed once: the router's arrival counter resets itself after every launch
+        self.scratch = torch.zeros(self.layout.total, dtype=torch.uint8, device=self.device)
+
+    def region(self, name: str, dtype, shape):
+        """A typed view of one scratch region (the launch's own intermediates)."""
+        at = getattr(self.layout, name)
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.scratch[at : at + nbytes].view(dtype).view(*shape)
+
+    def ffn(self, x: torch.Tensor, out: torch.Tensor, residual: torch.Tensor | None = None,
+            add_residual: bool = False, stream: torch.cuda.Stream | None = None) -> torch.Tensor:
+        b = self.build
+        rows = x.shape[0]
+        if not 1 <= rows <= b.width:
+            raise ValueError(f"rows={rows} outside 1..{b.width}")
+        _check(x, "x", torch.bfloat16, (rows, b.hidden))
+        _check(out, "out", torch.bfloat16, (rows, b.hidden))
+        if residual is not None:
+            _check(residual, "residual", torch.bfloat16, (rows, b.hidden))
+        # the scratch layout depends on the row count: lay out for the step's rows
+        lay = cabi.STRUCTS["B200MoeFfnLayout"]()
+        self.lib.call("moe_ffn_layout", rows, b.hidden, b.inter, b.experts, b.topk, lay)
+        self.step_layout = lay
+        a = cabi.fill(
+            "B200MoeFfnArgs", x=x, residual=residual, out=out, norm_w=self.w.norm, gate_w=self.w.gate_w,
+            gate_bias=self.w.bias, w13=self.w.w13, w13_scale=self.w.w13_s, w2=self.w.w2, w2_scale=self.w.w2_s,
+            scratch=self.scratch, scratch_bytes=self.scratch.numel(), rows=rows, hidden=b.hidden, inter=b.inter,
+            experts=b.experts, topk=b.topk, score_fn=b.score_fn, has_shared=int(b.has_shared),
+            add_residual=int(add_residual), eps=b.eps, route_scale=b.route_scale, swiglu_limit=b.swiglu_limit,
+        )
+        s = stream or torch.cuda.current_stream(self.device)
+        self.lib.call("moe_ffn", a, s.cuda_stream)
+        return out

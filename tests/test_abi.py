@@ -1,0 +1,73 @@
+"""The C-ABI library loads, exports every symbol the header declares, agrees with the
+binding about struct layouts, and rejects bad arguments with a message (no GPU needed:
+validation happens before any CUDA call)."""
+
+import ctypes
+
+import pytest
+
+import sgl_amd_mono_b200  # noqa: F401
+from sgl_amd_mono_b200 import cabi
+
+
+def test_exports_every_declared_symbol(lib):
+    assert len(cabi.FUNCTIONS) >= 12
+    for name in cabi.FUNCTIONS:
+        assert hasattr(lib.dll, name), name
+
+
+def test_struct_sizes_match(lib):
+    sizes = (ctypes.c_int32 * 64)()
+    n = lib.dll.b200mono_abi_sizes(sizes, 64)
+    assert n == len(cabi.STRUCTS)
+    assert list(sizes[:n]) == [ctypes.sizeof(s) for s in cabi.STRUCTS.values()]
+
+
+def test_layout_fixed_words_do_not_move(lib):
+    a, b = cabi.STRUCTS["B200MoeFfnLayout"](), cabi.STRUCTS["B200MoeFfnLayout"]()
+    lib.call("moe_ffn_layout", 1, 7168, 256, 256, 8, a)
+    lib.call("moe_ffn_layout", 32, 2048, 768, 64, 6, b)
+    assert (a.counter, a.union_count) == (b.counter, b.union_count) == (0, 256)
+    assert a.union_cap == 9 and b.union_cap == 65
+    offs = [getattr(b, f) for f, _ in cabi._STRUCT_FIELDS["B200MoeFfnLayout"] if f not in ("total", "union_cap", "pad_")]
+    assert all(o % 256 == 0 for o in offs) and b.total >= max(offs)
+
+
+@pytest.mark.parametrize(
+    "args",
+    [(0, 2048, 768, 64, 6), (33, 2048, 768, 64, 6), (4, 2000, 768, 64, 6), (4, 2048, 700, 64, 6),
+     (4, 2048, 768, 600, 6), (4, 2048, 768, 64, 17), (4, 2048, 768, 4, 6)],
+)
+def test_layout_rejects(lib, args):
+    out = cabi.STRUCTS["B200MoeFfnLayout"]()
+    with pytest.raises(cabi.B200MonoError) as e:
+        lib.call("moe_ffn_layout", *args, out)
+    assert e.value.code == cabi.ENUMS["B200MONO_E_ARG"] and "moe_ffn_layout" in str(e.value)
+
+
+def test_null_and_shape_rejection(lib):
+    with pytest.raises(cabi.B200MonoError, match="null pointer"):
+        lib.call("norm_quant", cabi.fill("B200NormQuantArgs", rows=1, hidden=128), None)
+    with pytest.raises(cabi.B200MonoError, match="multiple of 128"):
+        lib.call("gemv_fp8", cabi.fill("B200GemvFp8Args", w=256, w_scale=256, xq=256, x_scale=256, y=256,
+                                       rows=1, n=16, k=100, groups=1, ldy=16), None)
+    with pytest.raises(cabi.B200MonoError, match="rows=40"):
+        lib.call("gemv_fp8", cabi.fill("B200GemvFp8Args", w=256, w_scale=256, xq=256, x_scale=256, y=256,
+                                       rows=40, n=16, k=128, groups=1, ldy=16), None)
+    with pytest.raises(cabi.B200MonoError, match="32-byte"):
+        lib.call("gemv_fp8", cabi.fill("B200GemvFp8Args", w=272, w_scale=256, xq=256, x_scale=256, y=256,
+                                       rows=1, n=16, k=128, groups=1, ldy=16), None)
+    with pytest.raises(cabi.B200MonoError, match="score_fn"):
+        lib.call("router", cabi.fill("B200RouterArgs", x=256, gate_w=256, logits=256, topk_ids=256, topk_w=256,
+                                     union_count=256, union_ids=256, union_pick=256, counter=256, rows=1,
+                                     hidden=128, experts=8, topk=2, score_fn=2), None)
+    with pytest.raises(cabi.B200MonoError) as e:
+        lib.call("moe_ffn", cabi.fill("B200MoeFfnArgs", x=256, out=256, norm_w=256, gate_w=256, w13=256,
+                                      w13_scale=256, w2=256, w2_scale=256, scratch=256, scratch_bytes=16,
+                                      rows=4, hidden=2048, inter=768, experts=64, topk=6), None)
+    assert e.value.code == cabi.ENUMS["B200MONO_E_SCRATCH"]
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        cabi.Lib(str(tmp_path / "libb200mono.so"))

@@ -1,0 +1,256 @@
+"""GPU parity of the MoE FFN path through the C ABI against the oracle.
+
+Bit-exact where the arithmetic order is defined (norm, quant codes, router logits,
+routing, union), tolerance (stated per check) where only the f32 accumulation order of
+a GEMV differs.  Stage checks consume the launch's own intermediates, so an upstream
+rounding difference is never blamed downstream.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import sgl_amd_mono_b200  # noqa: F401
+from oracle import inputs
+from oracle import moe as M
+from oracle import quant as Q
+from sgl_amd_mono_b200 import cabi
+from sgl_amd_mono_b200.ffn import FfnBuild, FfnRunner, FfnWeights
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel(a, b):
+    a, b = a.detach().cpu().double().reshape(-1), b.detach().cpu().double().reshape(-1)
+    return ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+
+
+def u8(t):
+    return t.detach().cpu().contiguous().view(torch.uint8)
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+# ------------------------------------------------------------------ norm + quant
+@pytest.mark.parametrize("rows,hidden", [(1, 128), (4, 2048), (8, 7168), (32, 7168), (3, 6144)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_norm_quant_bit_exact(lib, rows, hidden, with_res):
+    x = inputs.rows_bf16(rows, hidden, seed=rows + hidden).to(DEV)
+    res = inputs.rows_bf16(rows, hidden, seed=5, scale=3.0).to(DEV) if with_res else None
+    w = (1 + 0.1 * torch.randn(hidden, generator=torch.Generator().manual_seed(3))).bfloat16().to(DEV)
+    if rows >= 4:
+        x[1] = 0  # an all-zero row: scale floor 1e-10/448, codes 0
+        if with_res:
+            res[1] = 0
+    y = torch.full((rows, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
+    so = torch.full_like(y, float("nan"))
+    q = torch.zeros(rows, hidden, dtype=torch.uint8, device=DEV)
+    qs = torch.full((rows, hidden // 128), float("nan"), device=DEV)
+    lib.call("norm_quant", cabi.fill("B200NormQuantArgs", x=x, residual=res, weight=w, res_out=so, y=y, q=q,
+                                     q_scale=qs, rows=rows, hidden=hidden, eps=1e-6, gemma=0), stream())
+    torch.cuda.synchronize()
+    s_ref, y_ref, q_ref, qs_ref = M.rmsnorm_quant(x, w, 1e-6, res)
+    assert torch.equal(u8(y), u8(y_ref)), f"normed rows differ in {(u8(y) != u8(y_ref)).sum().item()} bytes"
+    assert torch.equal(qs.cpu(), qs_ref)
+    assert torch.equal(q.cpu(), u8(q_ref))
+    if with_res:
+        assert torch.equal(u8(so), u8(s_ref))
+
+
+def test_quant128_bit_exact(lib):
+    x = inputs.rows_bf16(13, 768, seed=2, scale=2.0).to(DEV)
+    x[3, 128:256] = 0
+    for rule in (0, 1):
+        q = torch.zeros(13, 768, dtype=torch.uint8, device=DEV)
+        qs = torch.zeros(13, 6, device=DEV)
+        lib.call("quant128", cabi.fill("B200Quant128Args", x=x, q=q, q_scale=qs, rows=13, cols=768, zero_rule=rule), stream())
+        torch.cuda.synchronize()
+        q_ref, s_ref = Q.quant128(x.cpu(), zero_rule=bool(rule))
+        assert torch.equal(qs.cpu(), s_ref) and torch.equal(q.cpu(), u8(q_ref))
+
+
+# ------------------------------------------------------------------ block-FP8 GEMV
+GEMV_CASES = [
+    # rows, n, k, groups  (per-rank shapes of the sparse-MLA layer at TP8 and the small block)
+    (4, 1536, 2048, 1),   # small-block gate/up as a plain GEMV
+    (1, 2240, 7168, 1),   # q_a + kv_a + index key
+    (8, 3072, 1536, 1),   # q_b, 16 heads x 192
+    (8, 7168, 2048, 1),   # o_proj slice
+    (8, 8192, 128, 16),   # absorbed W_UK: 16 heads, 512 x 128 each
+    (8, 2048, 512, 16),   # W_UV: 16 heads, 128 x 512 each
+    (17, 256, 256, 1),    # two MMA column groups, ragged
+    (32, 512, 384, 1),    # four column groups, k blocks not divisible by the slices
+    (5, 16, 128, 1),      # one tile, one k block
+]
+
+
+@pytest.mark.parametrize("rows,n,k,groups", GEMV_CASES)
+def test_gemv_fp8_against_oracle(lib, rows, n, k, groups):
+    g = torch.Generator().manual_seed(n + k + rows)
+    wq, ws = Q.quant_weight_block128(0.02 * torch.randn(n, k, generator=g))
+    x = torch.randn(rows, groups * k, generator=g).bfloat16()
+    xq, xs = Q.quant128(x)
+    ref = Q.gemv_fp8(xq, xs, wq, ws, groups)
+    d = [t.to(DEV) for t in (wq, ws, xq, xs)]
+    for f32 in (1, 0):
+        y = torch.full((rows, n + 16), float("nan"), dtype=torch.float32 if f32 else torch.bfloat16, device=DEV)
+        lib.call("gemv_fp8", cabi.fill("B200GemvFp8Args", w=d[0], w_scale=d[1], xq=d[2], x_scale=d[3], y=y, rows=rows,
+                                       n=n, k=k, groups=groups, ldy=n + 16, y_f32=f32), stream())
+        torch.cuda.synchronize()
+        assert torch.isnan(y[:, n:].float()).all(), "wrote past n"
+        got = y[:, :n].float().cpu()
+        if f32:
+            assert rel(got, ref) < 2e-6, rel(got, ref)  # only the f32 summation order differs
+        else:
+            assert torch.equal(got, got.bfloat16().float()) and rel(got, ref) < 5e-3
+
+
+# ------------------------------------------------------------------ router
+ROUTER_CASES = [
+    (4, 2048, 64, 6, 0, True), (1, 7168, 256, 8, 1, True), (8, 7168, 256, 8, 1, True), (32, 7168, 256, 8, 1, True),
+    (8, 6144, 160, 8, 1, True), (32, 2048, 512, 10, 0, True), (5, 1024, 33, 3, 1, False),
+]
+
+
+@pytest.mark.parametrize("rows,hidden,experts,topk,score_fn,shared", ROUTER_CASES)
+def test_router_bit_exact(lib, rows, hidden, experts, topk, score_fn, shared):
+    g = torch.Generator().manual_seed(experts + rows)
+    x = torch.randn(rows, hidden, generator=g).bfloat16()
+    gw = (0.02 * torch.randn(experts, hidden, generator=g)).bfloat16()
+    bias = (0.02 * torch.randn(experts, generator=g)).float() if score_fn == 1 else None
+    if rows > 1:
+        gw[7] = gw[3]  # identical experts: a tie the lower id must win
+    logits = torch.full((rows, experts), float("nan"), device=DEV)
+    ids = torch.full((rows, topk), -1, dtype=torch.int32, device=DEV)
+    wts = torch.full((rows, topk), float("nan"), device=DEV)
+    ucount = torch.zeros(1, dtype=torch.int32, device=DEV)
+    uids = torch.full((experts + 1,), -1, dtype=torch.int32, device=DEV)
+    pick = torch.full((experts + 1, 32), 255, dtype=torch.uint8, device=DEV)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    xd, gd = x.to(DEV), gw.to(DEV)
+    bd = None if bias is None else bias.to(DEV)
+    args = cabi.fill("B200RouterArgs", x=xd, gate_w=gd, bias=bd, logits=logits, topk_ids=ids, topk_w=wts,
+                     union_count=ucount, union_ids=uids, union_pick=pick, counter=counter, rows=rows, hidden=hidden,
+                     experts=experts, topk=topk, score_fn=score_fn, route_scale=2.5, has_shared=int(shared))
+    for _ in range(2):  # the arrival counter must reset itself
+        lib.call("router", args, stream())
+    torch.cuda.synchronize()
+    assert int(counter.item()) == 0
+    l_ref = M.router_logits(x, gw)
+    assert np.array_equal(logits.cpu().numpy().view(np.uint32), l_ref.view(np.uint32)), "logit bits differ"
+    ids_ref, w_ref = M.route(l_ref, None if bias is None else bias.numpy(), topk, score_fn, 2.5)
+    assert np.array_equal(ids.cpu().numpy(), ids_ref)
+    assert np.array_equal(wts.cpu().numpy().view(np.uint32), w_ref.view(np.uint32)), "weight bits differ"
+    uni, pk = M.union_of(ids_ref, experts, shared)
+    U = int(ucount.item())
+    assert U == len(uni) and np.array_equal(uids.cpu().numpy()[:U], uni)
+    assert np.array_equal(pick.cpu().numpy()[:U], pk)
+    if rows > 1 and score_fn == 0:
+        for t in range(rows):
+            r = ids_ref[t].tolist()
+            if 7 in r:
+                assert 3 in r and r.index(3) < r.index(7)
+
+
+# ------------------------------------------------------------------ the whole block
+def _runner(cfg, w, width):
+    b = FfnBuild(width=width, hidden=cfg["hidden"], inter=cfg["inter"], experts=cfg["experts"], topk=cfg["topk"],
+                 score_fn=cfg["score_fn"], has_shared=cfg["has_shared"], route_scale=cfg["route_scale"], eps=cfg["eps"],
+                 swiglu_limit=cfg["swiglu_limit"])
+    fw = FfnWeights(norm=w["norm"], gate_w=w["gate_w"], bias=w["bias"], w13=w["w13"], w13_s=w["w13_s"], w2=w["w2"],
+                    w2_s=w["w2_s"])
+    return FfnRunner(b, fw, DEV)
+
+
+def _check_block(cfg, w, x, residual=None, add_residual=False, width=None):
+    """Run the launch and compare every intermediate with the oracle fed the same inputs."""
+    rows = x.shape[0]
+    r = _runner(cfg, w, width or rows)
+    out = torch.full_like(x, float("nan"))
+    r.ffn(x, out, residual, add_residual)
+    torch.cuda.synchronize()
+    L = r.step_layout
+    H, I, E, K = cfg["hidden"], cfg["inter"], cfg["experts"], cfg["topk"]
+
+    def reg(name, dtype, shape):
+        at = getattr(L, name)
+        n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        return r.scratch[at : at + n].view(dtype).view(*shape).cpu()
+
+    o = M.moe_ffn(x, w, cfg, residual, add_residual)
+    # bit-exact stages
+    assert torch.equal(u8(reg("xn", torch.bfloat16, (rows, H))), u8(o["xn"]))
+    assert torch.equal(reg("xq", torch.uint8, (rows, H)), u8(o["xq"]))
+    assert torch.equal(reg("xs", torch.float32, (rows, H // 128)), o["xs"])
+    assert np.array_equal(reg("logits", torch.float32, (rows, E)).numpy().view(np.uint32), o["logits"].view(np.uint32))
+    assert np.array_equal(reg("topk_ids", torch.int32, (rows, K)).numpy(), o["ids"])
+    assert np.array_equal(reg("topk_w", torch.float32, (rows, K)).numpy().view(np.uint32), o["wts"].view(np.uint32))
+    U = int(reg("union_count", torch.int32, (1,)).item())
+    assert U == len(o["union"])
+    assert np.array_equal(reg("union_ids", torch.int32, (E + 1,)).numpy()[:U], o["union"])
+    # the launch's own mid rows against the oracle's expert on the launch's own quantised input
+    mid = reg("mid", torch.bfloat16, (L.union_cap, rows, I))
+    worst = 0.0
+    for u, e in enumerate(o["union"].tolist()):
+        worst = max(worst, rel(mid[u], o["mids"][e]))
+    assert worst < 6e-3, worst  # bf16 rounding of a value whose f32 sum order differs
+    # requant of the launch's own mid is exact
+    mq, ms = Q.quant128(mid[:U].reshape(U * rows, I))
+    assert torch.equal(reg("midq", torch.uint8, (L.union_cap, rows, I))[:U].reshape(U * rows, I), u8(mq))
+    assert torch.equal(reg("mids", torch.float32, (L.union_cap, rows, I // 128))[:U].reshape(U * rows, -1), ms)
+    assert not torch.isnan(out.float()).any()
+    e = rel(out, o["out"])
+    assert e < 2e-2, e  # bf16 hidden after FP8 quant
+    return out, o, e
+
+
+def test_c1_block_against_oracle(lib):
+    cfg = inputs.C1
+    w = inputs.moe_weights(cfg, seed=0, device=DEV)
+    x = inputs.rows_bf16(cfg["rows"], cfg["hidden"], seed=0).to(DEV)
+    out, o, e = _check_block(cfg, w, x)
+    assert e < 5e-3, e
+
+
+def test_c1_block_residual_width_and_row_independence(lib):
+    cfg = inputs.C1
+    w = inputs.moe_weights(cfg, seed=1, device=DEV)
+    x = inputs.rows_bf16(8, cfg["hidden"], seed=1).to(DEV)
+    res = inputs.rows_bf16(8, cfg["hidden"], seed=2).to(DEV)
+    out, _, _ = _check_block(cfg, w, x, res, True, width=32)
+    # a row's output does not depend on the other rows or on the width
+    one, _, _ = _check_block(cfg, w, x[5:6].contiguous(), res[5:6].contiguous(), True, width=8)
+    assert torch.equal(one[0], out[5])
+    # replays are bitwise identical
+    r = _runner(cfg, w, 8)
+    a, b = torch.empty_like(x), torch.empty_like(x)
+    r.ffn(x, a, res, True)
+    for _ in range(20):
+        r.ffn(x, b, res, True)
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("rows", [1, 8, 32])
+def test_c2_tp8_ffn_against_oracle(lib, rows):
+    cfg = inputs.c2_ffn(8, rows)
+    w = inputs.moe_weights(cfg, seed=2, device=DEV, experts_chunk=32)
+    x = inputs.rows_bf16(rows, cfg["hidden"], seed=rows).to(DEV)
+    res = inputs.rows_bf16(rows, cfg["hidden"], seed=40 + rows).to(DEV)
+    _check_block(cfg, w, x, res, True)
+
+
+def test_negative_control_scale_error_is_caught(lib):
+    """A doubled weight scale must push the block outside its tolerance."""
+    cfg = inputs.C1
+    w = inputs.moe_weights(cfg, seed=0, device=DEV)
+    x = inputs.rows_bf16(4, cfg["hidden"], seed=0).to(DEV)
+    good = M.moe_ffn(x, w, cfg)["out"]
+    w2 = dict(w, w2_s=w["w2_s"] * 2)
+    r = _runner(cfg, w2, 4)
+    out = torch.empty_like(x)
+    r.ffn(x, out)
+    torch.cuda.synchronize()
+    assert rel(out, good) > 0.5
