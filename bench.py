@@ -222,31 +222,32 @@ def run_ours(args):
     e2e_us = timed(e2e_step, args.steps) * 1000.0 / args.steps
     row_bytes = args.rows * cfg["hidden"] * 2
 
-    # ---- the dominant kernel (expert gate/up GEMV), timed alone over the same steps
+    # ---- every kernel of the step timed alone over the same steps (separate C-ABI calls, CUDA events
+    # around each on its stream, L2 flushed before each step)
     up_b, down_b = expert_bytes(cfg)
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    unions = []
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    names = ["norm_quant", "router", "moe_up", "quant128", "moe_down"]
+    per_stage = {n: [] for n in names}
+    unions, evs = [], []
     with torch.cuda.stream(stream):
         for i in range(args.steps):
             r = layers[i % args.layers]
-            r.ffn(xs[i % n_in], out, res, True, stream=stream)  # fills this step's routing and xq
-            L = r.step_layout
-            sc = r.scratch
-            a = cabi.fill("B200MoeUpArgs", xq=sc[L.xq:], x_scale=sc[L.xs:], w13=r.w.w13, w13_scale=r.w.w13_s,
-                          union_count=sc[L.union_count:], union_ids=sc[L.union_ids:], mid=sc[L.mid:], rows=args.rows,
-                          hidden=cfg["hidden"], inter=cfg["inter"], experts=cfg["experts"], union_cap=L.union_cap,
-                          swiglu_limit=0.0)
-            # evict the weights the warm-up call above pulled into L2
-            flush = getattr(run_ours, "_flush", None)
-            if flush is None:
-                flush = run_ours._flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+            calls = r.stage_calls(xs[i % n_in], out, res, True)
             flush.zero_()
-            ev[i][0].record(stream)
-            lib.call("moe_up", a, stream.cuda_stream)
-            ev[i][1].record(stream)
-            unions.append(sc[L.union_count:L.union_count + 4].view(torch.int32).clone())
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(len(calls) + 1)]
+            marks[0].record(stream)
+            for j, (name, a) in enumerate(calls):
+                lib.call(name, a, stream.cuda_stream)
+                marks[j + 1].record(stream)
+            evs.append(marks)
+            L = r.step_layout
+            unions.append(r.scratch[L.union_count:L.union_count + 4].view(torch.int32).clone())
         stream.synchronize()
-    up_us = [a.elapsed_time(b) * 1000.0 for a, b in ev]
+    for marks in evs:
+        for j, n in enumerate(names):
+            per_stage[n].append(marks[j].elapsed_time(marks[j + 1]) * 1000.0)
+    stage_us = {n: round(statistics.mean(v), 2) for n, v in per_stage.items()}
+    up_us = per_stage["moe_up"]
     u_mean = float(sum(int(u.item()) for u in unions)) / len(unions)
     up_bytes = u_mean * up_b
     peak, peak_kind = peaks()
@@ -268,10 +269,11 @@ def run_ours(args):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
         "roofline": {
-            "bound": "hbm", "kernel": "gemv_kernel<2,NT> (expert gate/up GEMV + SwiGLU)", "achieved": round(up_gbs, 1),
+            "bound": "hbm", "kernel": "stream_kernel<NT,SWIGLU> (expert gate/up GEMV + SwiGLU, TMA ring)", "achieved": round(up_gbs, 1),
             "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(up_gbs / peak, 4), "traffic": None,
             "bytes_per_launch": up_bytes, "us_per_launch": round(statistics.mean(up_us), 3),
             "timed": "second pass over the same steps, CUDA events around the kernel on its stream, L2 flushed before each",
+            "stages_us": stage_us, "down_gbs": round(u_mean * down_b / (stage_us["moe_down"] * 1e-6) / 1e9, 1),
             "step_bytes": layer_bytes, "step_frac_of_hbm_roofline": round(layer_bytes / (us_per_step * 1e-6) / 1e9 / peak, 4),
         },
     }

@@ -115,6 +115,9 @@ typedef struct {
   int32_t groups;       /* >= 1, n % (16*groups) == 0 */
   int32_t ldy;          /* elements between output rows (>= n) */
   int32_t y_f32;        /* 1: y is f32 */
+  uint32_t* status;     /* u32 [1] or NULL: set to (site<<16 | cta) by a device wait that gave up */
+  int32_t variant;      /* 0: pick automatically; 1: register-pipelined kernel; 2: persistent TMA-ring kernel */
+  int32_t pad_;
 } B200GemvFp8Args;
 int b200mono_gemv_fp8(const B200GemvFp8Args* a, void* stream);
 
@@ -123,14 +126,16 @@ int b200mono_gemv_fp8(const B200GemvFp8Args* a, void* stream);
  * top-k (ties -> smaller expert id), weights, and the union of picked experts.
  * Replaces stage_router/stage_route (sgl_amd_mono/deepseek_v41/gfx950/stages/moe.py:267-390)
  * and route_top8 (sgl_amd_mono/glm53/gfx950/kernel.py:1926-1999).
- * Order of the f32 logit sum for (row t, expert e): lane l of a warp adds the
- * products of columns 8*(l + 32*i) + j for i = 0.., j = 0..7 in that order;
- * the 32 lane sums meet in an xor tree (16, 8, 4, 2, 1).
+ * Order of the f32 logit sum for (row t, expert e): the columns are cut into
+ * chunks of 1024; inside a chunk lane l of a warp adds the products of columns
+ * 1024*ch + 8*(l + 32*i) + j for i = 0..3, j = 0..7 in that order and the 32 lane
+ * sums meet in an xor tree (16, 8, 4, 2, 1); the chunk sums are added in chunk order.
  */
 typedef struct {
   const void* x;          /* bf16 [rows, hidden] (the normed activations) */
   const void* gate_w;     /* bf16 [experts, hidden] */
   const float* bias;      /* f32 [experts] or NULL (selection bias) */
+  float* logit_parts;     /* f32 [rows, experts, ceil(hidden/1024)] scratch */
   float* logits;          /* f32 [rows, experts] out */
   int32_t* topk_ids;      /* int32 [rows, topk] out, in rank order */
   float* topk_w;          /* f32 [rows, topk] out */
@@ -166,6 +171,9 @@ typedef struct {
   int32_t rows, hidden, inter, experts;
   int32_t union_cap;        /* upper bound of U the grid is sized for: min(rows*topk, experts) + 1 */
   float swiglu_limit;
+  uint32_t* status;         /* u32 [1] or NULL: as in B200GemvFp8Args */
+  int32_t variant;          /* as in B200GemvFp8Args */
+  int32_t pad_;
 } B200MoeUpArgs;
 int b200mono_moe_up(const B200MoeUpArgs* a, void* stream);
 
@@ -193,7 +201,7 @@ int b200mono_moe_down(const B200MoeDownArgs* a, void* stream);
  * normed rows, logits, routing and mid values.
  */
 typedef struct {
-  int64_t res, xn, xq, xs, logits, topk_ids, topk_w, union_count, union_ids, union_pick, counter,
+  int64_t status, res, xn, xq, xs, logit_parts, logits, topk_ids, topk_w, union_count, union_ids, union_pick, counter,
       mid, midq, mids, total;
   int32_t union_cap, pad_;
 } B200MoeFfnLayout;

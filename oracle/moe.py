@@ -58,28 +58,32 @@ def rmsnorm_quant(x, weight, eps, residual=None, gemma=False):
 
 
 def router_logits(xn: torch.Tensor, gate_w: torch.Tensor) -> np.ndarray:
-    """f32 logits [rows, E] in the kernel's order: lane l of 32 adds the products of
-    columns 8*(l + 32 i) + j, i ascending, j = 0..7; then the xor tree.
+    """f32 logits [rows, E] in the kernel's order: columns in chunks of 1024; inside a chunk
+    lane l of 32 adds the products of columns 8*(l + 32 i) + j, i = 0..3, j = 0..7, then the xor
+    tree; chunk sums added in chunk order.
     (The reference fixes its own order the same way: K parts summed in wave order,
     sgl_amd_mono/deepseek_v41/gfx950/stages/router.py:1-6.)"""
     x, w = _np(xn), _np(gate_w)
     rows, hidden = x.shape
     E = w.shape[0]
-    nvec = hidden // 8
-    per = -(-nvec // 32)
-    out = np.empty((rows, E), np.float32)
-    wp = np.zeros((E, per * 32 * 8), np.float32)
+    nch = -(-hidden // 1024)
+    wp = np.zeros((E, nch * 1024), np.float32)
     wp[:, :hidden] = w
-    wp = wp.reshape(E, per, 32, 8)
+    wp = wp.reshape(E, nch, 4, 32, 8)
+    out = np.empty((rows, E), np.float32)
     for t in range(rows):
-        xp = np.zeros(per * 32 * 8, np.float32)
+        xp = np.zeros(nch * 1024, np.float32)
         xp[:hidden] = x[t]
-        xp = xp.reshape(per, 32, 8)
-        acc = np.zeros((E, 32), np.float32)
-        for i in range(per):
+        xp = xp.reshape(nch, 4, 32, 8)
+        acc = np.zeros((E, nch, 32), np.float32)
+        for i in range(4):
             for j in range(8):
-                acc = (acc + (wp[:, i, :, j] * xp[None, i, :, j]).astype(np.float32)).astype(np.float32)
-        out[t] = dm.warp_sum_tree(acc)
+                acc = (acc + (wp[:, :, i, :, j] * xp[None, :, i, :, j]).astype(np.float32)).astype(np.float32)
+        parts = dm.warp_sum_tree(acc)  # [E, nch]
+        tot = parts[:, 0]
+        for ch in range(1, nch):
+            tot = (tot + parts[:, ch]).astype(np.float32)
+        out[t] = tot
     return out
 
 

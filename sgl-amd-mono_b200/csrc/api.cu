@@ -99,12 +99,19 @@ int b200mono_gemv_fp8(const B200GemvFp8Args* a, void* stream) {
           "gemv_fp8: rows per group must divide or be a multiple of 128");
   REQUIRE(a->ldy >= a->n, "gemv_fp8: ldy=%d < n=%d", a->ldy, a->n);
   REQUIRE(aligned(a->w, 32) && aligned(a->xq, 16), "gemv_fp8: w must be 32-byte and xq 16-byte aligned");
+  // the TMA ring wants whole 32-row units inside one group and enough k blocks to fill a stage
+  const bool ring_ok = (a->groups == 1 || (a->n / a->groups) % 32 == 0) && a->k % 512 == 0 &&
+                       aligned(a->w_scale, 16) && aligned(a->x_scale, 16);
+  REQUIRE(a->variant >= 0 && a->variant <= 2 && (a->variant != 2 || ring_ok),
+          "gemv_fp8: variant=%d not available for this shape", a->variant);
+  const bool ring = a->variant == 2 || (a->variant == 0 && ring_ok && a->k >= 1024);
+  if (ring) return cuda_status(launch_gemv_stream(*a, a->status, (cudaStream_t)stream), "gemv_fp8(ring)");
   return cuda_status(launch_gemv_fp8(*a, (cudaStream_t)stream), "gemv_fp8");
 }
 
 int b200mono_router(const B200RouterArgs* a, void* stream) {
   REQUIRE(a, "router: null args");
-  REQUIRE(a->x && a->gate_w && a->logits && a->topk_ids && a->topk_w && a->union_count &&
+  REQUIRE(a->x && a->gate_w && a->logits && a->logit_parts && a->topk_ids && a->topk_w && a->union_count &&
               a->union_ids && a->union_pick && a->counter,
           "router: null pointer");
   REQUIRE(a->rows >= 1 && a->rows <= 32, "router: rows=%d outside 1..32", a->rows);
@@ -134,6 +141,11 @@ int b200mono_moe_up(const B200MoeUpArgs* a, void* stream) {
   REQUIRE(a->union_cap >= 1 && a->union_cap <= a->experts + 1, "moe_up: union_cap=%d outside 1..experts+1",
           a->union_cap);
   REQUIRE(aligned(a->xq, 16) && aligned(a->w13, 32), "moe_up: w13 must be 32-byte and xq 16-byte aligned");
+  REQUIRE(a->variant >= 0 && a->variant <= 2, "moe_up: variant=%d outside 0..2", a->variant);
+  const bool ring_ok = a->hidden % 512 == 0 && aligned(a->w13_scale, 16) && aligned(a->x_scale, 16);
+  REQUIRE(a->variant != 2 || ring_ok, "moe_up: variant=2 not available for this shape");
+  if (a->variant != 1 && ring_ok)
+    return cuda_status(launch_moe_up_stream(*a, a->status, (cudaStream_t)stream), "moe_up(ring)");
   return cuda_status(launch_moe_up(*a, (cudaStream_t)stream), "moe_up");
 }
 
@@ -164,10 +176,12 @@ int b200mono_moe_ffn_layout(int32_t rows, int32_t hidden, int32_t inter, int32_t
   // because the arrival counter has to stay zero between launches of any width
   out->counter = take(4);
   out->union_count = take(4);
+  out->status = take(4);
   out->res = take((int64_t)rows * hidden * 2);
   out->xn = take((int64_t)rows * hidden * 2);
   out->xq = take((int64_t)rows * hidden);
   out->xs = take((int64_t)rows * (hidden / 128) * 4);
+  out->logit_parts = take((int64_t)rows * experts * ((hidden + 1023) / 1024) * 4);
   out->logits = take((int64_t)rows * experts * 4);
   out->topk_ids = take((int64_t)rows * topk * 4);
   out->topk_w = take((int64_t)rows * topk * 4);
@@ -214,6 +228,7 @@ int b200mono_moe_ffn(const B200MoeFfnArgs* a, void* stream) {
   r.x = sc + L.xn;
   r.gate_w = a->gate_w;
   r.bias = a->gate_bias;
+  r.logit_parts = (float*)(sc + L.logit_parts);
   r.logits = (float*)(sc + L.logits);
   r.topk_ids = (int32_t*)(sc + L.topk_ids);
   r.topk_w = (float*)(sc + L.topk_w);
@@ -244,6 +259,8 @@ int b200mono_moe_ffn(const B200MoeFfnArgs* a, void* stream) {
   up.experts = a->experts;
   up.union_cap = L.union_cap;
   up.swiglu_limit = a->swiglu_limit;
+  up.status = (uint32_t*)(sc + L.status);
+  up.variant = 0;
   if (int rc = b200mono_moe_up(&up, s)) return rc;
 
   B200Quant128Args q{};

@@ -15,6 +15,9 @@ cudaError_t launch_router(const B200RouterArgs& a, cudaStream_t s);
 cudaError_t launch_gemv_fp8(const B200GemvFp8Args& a, cudaStream_t s);
 cudaError_t launch_moe_up(const B200MoeUpArgs& a, cudaStream_t s);
 cudaError_t launch_moe_down(const B200MoeDownArgs& a, cudaStream_t s);
+// persistent TMA-ring forms; `status` (may be null) receives the site of a wait that gave up
+cudaError_t launch_moe_up_stream(const B200MoeUpArgs& a, uint32_t* status, cudaStream_t s);
+cudaError_t launch_gemv_stream(const B200GemvFp8Args& a, uint32_t* status, cudaStream_t s);
 
 // upper bound of distinct experts a step can pick (+1 shared)
 inline int union_capacity(int rows, int topk, int experts, int has_shared) {

@@ -161,7 +161,9 @@ cudaError_t launch_quant128(const B200Quant128Args& a, cudaStream_t s) {
 }
 
 // ------------------------------------------------------------------ router
-// Phase 1 (all CTAs): warp per expert, logits for every row in the stated order.
+// Phase 1 (all CTAs): warp per (expert, 1024-column chunk): per-chunk partial logits for
+// every row in the stated order, enough independent loads in flight to stream the gate
+// matrix at full rate.
 // Phase 2 (the CTA that arrives last): warp per row, score + exact top-k by
 // (key descending, expert id ascending) + weights; then the union of picked
 // experts in ascending id order and, per union entry, which slot of which row
@@ -172,17 +174,28 @@ template <int MAXT>
 __global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int T = a.rows, E = a.experts, H = a.hidden;
+  // Phase 1: warp per (expert, 1024-column chunk); four independent 16-byte loads per lane.
+  const int nch = (H + 1023) >> 10;
   {
-    const int e = blockIdx.x * 8 + warp;
-    if (e < E) {
+    const int item = blockIdx.x * 8 + warp;
+    if (item < E * nch) {
+      const int e = item / nch, ch = item % nch;
       float acc[MAXT];
 #pragma unroll
       for (int t = 0; t < MAXT; ++t) acc[t] = 0.f;
       const uint4* wrow = reinterpret_cast<const uint4*>(a.gate_w) + (size_t)e * (H >> 3);
       const uint4* xb = reinterpret_cast<const uint4*>(a.x);
-      for (int v = lane; v < (H >> 3); v += 32) {
-        uint4 wv = ld_stream_u4(wrow + v);
-        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint4 wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int v = ch * 128 + lane + 32 * i;
+        wv[i] = v < (H >> 3) ? ld_stream_u4(wrow + v) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int v = ch * 128 + lane + 32 * i;
+        if (v >= (H >> 3)) continue;
+        const uint32_t ww[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
 #pragma unroll
         for (int t = 0; t < MAXT; ++t) {
           if (t < T) {
@@ -201,7 +214,7 @@ __global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a) {
       for (int t = 0; t < MAXT; ++t) {
         if (t < T) {
           float v = warp_sum_tree(acc[t]);
-          if (lane == 0) a.logits[(size_t)t * E + e] = v;
+          if (lane == 0) a.logit_parts[((size_t)t * E + e) * nch + ch] = v;
         }
       }
     }
@@ -236,7 +249,11 @@ __global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a) {
       score[j] = 0.f;
       key[j] = 0;
       if (e < E) {
-        float l = __ldcg(a.logits + (size_t)t * E + e);
+        // chunk sums in chunk order
+        const float* parts = a.logit_parts + ((size_t)t * E + e) * nch;
+        float l = __ldcg(parts);
+        for (int ch = 1; ch < nch; ++ch) l = __fadd_rn(l, __ldcg(parts + ch));
+        a.logits[(size_t)t * E + e] = l;
         if (a.score_fn == B200MONO_SCORE_SOFTMAX) {
           score[j] = l;
           key[j] = radix_key(l);
@@ -331,7 +348,7 @@ __global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a) {
 }
 
 cudaError_t launch_router(const B200RouterArgs& a, cudaStream_t s) {
-  const unsigned grid = (unsigned)((a.experts + 7) / 8);
+  const unsigned grid = (unsigned)((a.experts * ((a.hidden + 1023) / 1024) + 7) / 8);
   if (a.rows <= 8)
     router_kernel<8><<<grid, 256, 0, s>>>(a);
   else if (a.rows <= 16)

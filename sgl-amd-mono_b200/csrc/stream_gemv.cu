@@ -1,0 +1,420 @@
+// Persistent weight-streaming GEMV: one CTA per SM, a TMA-fed shared-memory
+// ring, tensor-core consumers.
+//
+// Work unit = 32 weight rows x the whole K: two 16-row MMA row sets (gate tile
+// + up tile of one expert for the SwiGLU form, two consecutive output tiles
+// for the plain form).  One elected producer lane fills a ring stage with six
+// TMA copies: two tiled tensor copies of 16 rows x 1 KiB of weights
+// (cp.async.bulk.tensor.2d over a tensor map of the weight matrix in its
+// checkpoint layout, viewed as u32 so that a box row can be 1 KiB), one tensor
+// copy of the matching 1 KiB of every activation row, one of the activation
+// rows' 8 block scales, and two small bulk copies of the weight row sets'
+// 8 block scales.  (Issuing one bulk copy per weight row instead costs about
+// 50 ns of issue time per copy and caps the ring at ~3 TB/s; 16 KiB boxes do
+// not.)  The consumers touch nothing but shared memory between two barriers,
+// so no global-memory latency sits on the path that frees a stage.  A stage
+// is 32 KiB of weights (+ 8 KiB of activations at 8 rows); the ring keeps
+// ~160 KiB of loads in flight per SM, independent of register pressure, and
+// keeps running across unit boundaries.  Consumer warp w multiplies k block w
+// of the stage (all 32 rows), applies the 128x128 f32 block scale on the
+// accumulator, and after the last stage of a unit the 8 warps' partials are
+// summed in warp order through shared memory (so results are identical on
+// every launch).  Rows past the matrix edge and k blocks past K are zero-filled
+// by the TMA unit.
+#include <cuda.h>
+
+#include "gemv.cuh"
+#include "launch.h"
+#include "tma_ring.cuh"
+
+namespace b200mono {
+
+constexpr int kChunk = 1024;        // bytes per row per stage
+constexpr int kRowStride = kChunk;  // dense: the TMA box is written row after row
+constexpr int kConsumers = 8;            // warps
+constexpr int kThreads = (kConsumers + 1) * 32;
+
+enum { MODE_PLAIN = 0, MODE_SWIGLU = 1 };
+
+struct StreamP {
+  const uint8_t* w;
+  const float* ws;
+  const uint8_t* x;
+  const float* xs;
+  void* y;
+  int rows, n, k, groups, ldy, y_f32;
+  int inter;  // SWIGLU: rows between gate row and up row
+  int tiles;  // SWIGLU: inter/16 units per expert;  PLAIN: ceil(n/32) units
+  const int* union_count;
+  const int* union_ids;
+  long long w_stride_e, ws_stride_e, y_stride_u;
+  float limit;
+  uint32_t* status;
+  int stages;
+};
+
+template <int NT>
+constexpr int red_floats() {
+  return kConsumers * 2 * NT * 4 * 32;
+}
+// stage: [32 weight rows][NT*8 activation rows] (padded rows), [NT*8][8] activation scales, [2][8] weight scales
+template <int NT>
+constexpr int off_xscale() {
+  return (32 + NT * 8) * kRowStride;
+}
+template <int NT>
+constexpr int off_wscale() {
+  return off_xscale<NT>() + NT * 8 * 32;
+}
+template <int NT>
+constexpr int stage_bytes() {
+  return (off_wscale<NT>() + 64 + 127) / 128 * 128;
+}
+
+// Where a unit's operands live (same arithmetic for producer and consumers).
+struct UnitRef {
+  int wrow[2];          // first weight row of each row set (row coordinate of the tensor map)
+  const float* wsc[2];  // scale rows of the two row sets
+  int group;            // activation column group
+  char* y;
+  int col0[2];
+};
+
+template <int MODE>
+__device__ __forceinline__ UnitRef unit_ref(const StreamP& p, int unit, int KB) {
+  UnitRef r;
+  r.y = reinterpret_cast<char*>(p.y);
+  r.group = 0;
+  if (MODE == MODE_SWIGLU) {
+    const int u = unit / p.tiles, j = unit % p.tiles;
+    const int e = p.union_ids[u];
+    r.wrow[0] = e * 2 * p.inter + j * 16;
+    r.wrow[1] = r.wrow[0] + p.inter;
+    const float* wse = p.ws + (long long)e * p.ws_stride_e;
+    r.wsc[0] = wse + (size_t)((j * 16) >> 7) * KB;
+    r.wsc[1] = wse + (size_t)((p.inter + j * 16) >> 7) * KB;
+    r.y += (long long)u * p.y_stride_u;
+    r.col0[0] = r.col0[1] = j * 16;
+  } else {
+    const int n0 = unit * 32;
+    r.wrow[0] = n0;
+    r.wrow[1] = n0 + 16;  // past the last row: the TMA unit fills zeros
+    r.wsc[0] = p.ws + (size_t)(n0 >> 7) * KB;
+    r.wsc[1] = n0 + 16 < p.n ? p.ws + (size_t)((n0 + 16) >> 7) * KB : r.wsc[0];
+    r.group = n0 / (p.n / p.groups);
+    r.col0[0] = n0;
+    r.col0[1] = n0 + 16;
+  }
+  return r;
+}
+
+template <int NT, int MODE>
+__global__ __launch_bounds__(kThreads, 1) void stream_kernel(StreamP p, const __grid_constant__ CUtensorMap tm_w,
+                                                             const __grid_constant__ CUtensorMap tm_x,
+                                                             const __grid_constant__ CUtensorMap tm_xs) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int SB = stage_bytes<NT>();
+  // layout: [stages x SB][red: 2 buffers][barriers]
+  uint8_t* ring = smem;
+  float* red = reinterpret_cast<float*>(smem + (size_t)p.stages * SB);
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * red_floats<NT>());
+  uint64_t* empty = full + p.stages;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumers);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  WaitCtx ctx{&abort_flag, p.status};
+
+  const int KB = p.k >> 7;
+  const int nchunks = (p.k + kChunk - 1) / kChunk;
+  const int T = p.rows;
+  int total_units;
+  if (MODE == MODE_SWIGLU)
+    total_units = (*p.union_count) * p.tiles;
+  else
+    total_units = p.tiles;
+
+  if (warp == kConsumers) {
+    // ------------------------------------------------------------ producer (one elected lane issues)
+    const uint64_t stream_policy = policy_evict_first();
+    const uint64_t keep_policy = policy_evict_last();
+    uint32_t it = 0;
+    constexpr uint32_t kTileBytes = 2u * 16u * kChunk + NT * 8u * kChunk + NT * 8u * 32u;
+    for (int unit = blockIdx.x; unit < total_units && !abort_flag; unit += gridDim.x) {
+      const UnitRef u = unit_ref<MODE>(p, unit, KB);
+      for (int c = 0; c < nchunks; ++c, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1;
+        // warp-uniform decision: no lane may leave while others go on
+        if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1, ctx, 1))) break;
+        if (lane == 0) {
+          const uint32_t nkb = (uint32_t)min(8, KB - c * 8);
+          const uint32_t sbytes = nkb * 4;  // one f32 scale per k block
+          uint8_t* st = ring + (size_t)s * SB;
+          mbar_arrive_expect_tx(&full[s], kTileBytes + 2u * sbytes);
+          const int kcol = c * (kChunk / 4);  // u32 column
+          tma_2d(st, &tm_w, kcol, u.wrow[0], &full[s], stream_policy);
+          tma_2d(st + 16 * kChunk, &tm_w, kcol, u.wrow[1], &full[s], stream_policy);
+          tma_2d(st + 32 * kChunk, &tm_x, u.group * (p.k / 4) + kcol, 0, &full[s], keep_policy);
+          tma_2d(st + off_xscale<NT>(), &tm_xs, u.group * KB + c * 8, 0, &full[s], keep_policy);
+          bulk_g2s(st + off_wscale<NT>(), u.wsc[0] + c * 8, sbytes, &full[s], keep_policy);
+          bulk_g2s(st + off_wscale<NT>() + 32, u.wsc[1] + c * 8, sbytes, &full[s], keep_policy);
+        }
+        __syncwarp();
+      }
+    }
+    // drain: every stage armed but not yet consumed still has copies in flight towards this CTA
+    if (abort_flag) {
+      const uint32_t first = it > (uint32_t)S ? it - S : 0;
+      for (uint32_t i = first; i < it; ++i) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (!mbar_try_wait(&full[i % S], (i / S) & 1) && globaltimer_ns() - t0 < 10000000ull) {
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int g = lane >> 2, c4 = lane & 3;
+  uint32_t it = 0;
+  int buf = 0;
+  bool dead = false;
+  for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+    const UnitRef u = unit_ref<MODE>(p, unit, KB);
+    float acc[2][NT][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[r][nt][i] = 0.f;
+
+    for (int c = 0; c < nchunks; ++c, ++it) {
+      const int s = it % S;
+      const uint32_t ph = (it / S) & 1;
+      const bool active = c * 8 + warp < KB;
+      if (!__all_sync(0xffffffffu, mbar_wait(&full[s], ph, ctx, 2))) {
+        dead = true;
+        break;
+      }
+      if (active) {
+        const uint32_t st = smem_u32(ring + (size_t)s * SB);
+        const uint32_t frag = st + warp * 128 + c4 * 32;
+        uint4 x0[NT], x1[NT];
+        float s0[NT], s1[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint32_t xa = frag + (32 + nt * 8 + g) * kRowStride;
+          x0[nt] = lds_u4(xa);
+          x1[nt] = lds_u4(xa + 16);
+          s0[nt] = lds_f32(st + off_xscale<NT>() + (nt * 8 + 2 * c4) * 32 + warp * 4);
+          s1[nt] = lds_f32(st + off_xscale<NT>() + (nt * 8 + 2 * c4 + 1) * 32 + warp * 4);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float wsr = lds_f32(st + off_wscale<NT>() + r * 32 + warp * 4);
+          const uint32_t lo_addr = frag + (r * 16 + g) * kRowStride;
+          const uint32_t hi_addr = lo_addr + 8 * kRowStride;
+          const uint4 lo0 = lds_u4(lo_addr), lo1 = lds_u4(lo_addr + 16);
+          const uint4 hi0 = lds_u4(hi_addr), hi1 = lds_u4(hi_addr + 16);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            float q[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_e4m3_16x8x32(q, lo0.x, hi0.x, lo0.y, hi0.y, x0[nt].x, x0[nt].y);
+            mma_e4m3_16x8x32(q, lo0.z, hi0.z, lo0.w, hi0.w, x0[nt].z, x0[nt].w);
+            mma_e4m3_16x8x32(q, lo1.x, hi1.x, lo1.y, hi1.y, x1[nt].x, x1[nt].y);
+            mma_e4m3_16x8x32(q, lo1.z, hi1.z, lo1.w, hi1.w, x1[nt].z, x1[nt].w);
+            const float f0 = wsr * s0[nt], f1 = wsr * s1[nt];
+            acc[r][nt][0] = fmaf(q[0], f0, acc[r][nt][0]);
+            acc[r][nt][1] = fmaf(q[1], f1, acc[r][nt][1]);
+            acc[r][nt][2] = fmaf(q[2], f0, acc[r][nt][2]);
+            acc[r][nt][3] = fmaf(q[3], f1, acc[r][nt][3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+    }
+
+    // ---- cross-warp reduction in warp order + epilogue, spread over the 256 consumer threads
+    float* rb = red + (size_t)buf * red_floats<NT>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rb[((warp * 2 + r) * NT * 4 + nt * 4 + i) * 32 + lane] = acc[r][nt][i];
+    // every consumer takes the same exit: the barrier also ORs the "a wait gave up" bits
+    if (named_bar_or(1, kConsumers * 32, dead)) return;
+    if (MODE == MODE_SWIGLU) {
+      for (int o = threadIdx.x; o < NT * 128; o += kConsumers * 32) {
+        const int nt = o >> 7, i = (o >> 5) & 3, ln = o & 31;
+        float gate = 0.f, up = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumers; ++w) {
+          gate += rb[((w * 2 + 0) * NT * 4 + nt * 4 + i) * 32 + ln];
+          up += rb[((w * 2 + 1) * NT * 4 + nt * 4 + i) * 32 + ln];
+        }
+        const int t = nt * 8 + 2 * (ln & 3) + (i & 1);
+        const int col = u.col0[0] + (ln >> 2) + ((i & 2) ? 8 : 0);
+        if (t < T) {
+          if (p.limit > 0.f) {
+            gate = fminf(gate, p.limit);
+            up = fminf(fmaxf(up, -p.limit), p.limit);
+          }
+          reinterpret_cast<__nv_bfloat16*>(u.y)[(size_t)t * p.ldy + col] = __float2bfloat16_rn(det_silu(gate) * up);
+        }
+      }
+    } else {
+      for (int o = threadIdx.x; o < 2 * NT * 128; o += kConsumers * 32) {
+        const int r = o / (NT * 128), oo = o % (NT * 128);
+        const int nt = oo >> 7, i = (oo >> 5) & 3, ln = oo & 31;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumers; ++w) v += rb[((w * 2 + r) * NT * 4 + nt * 4 + i) * 32 + ln];
+        const int t = nt * 8 + 2 * (ln & 3) + (i & 1);
+        const int col = u.col0[r] + (ln >> 2) + ((i & 2) ? 8 : 0);
+        if (t < T && col < p.n) {
+          if (p.y_f32)
+            reinterpret_cast<float*>(u.y)[(size_t)t * p.ldy + col] = v;
+          else
+            reinterpret_cast<__nv_bfloat16*>(u.y)[(size_t)t * p.ldy + col] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+    buf ^= 1;
+  }
+}
+
+// ---------------------------------------------------------------- host: tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// 2-D map over a row-major matrix of 4-byte words: `cols` words per row, `pitch` bytes between rows.
+static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, uint64_t cols, uint64_t rows,
+                     uint64_t pitch, uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int NT, int MODE>
+static cudaError_t launch_stream_nt(StreamP p, int grid, long long w_rows, cudaStream_t s) {
+  const size_t budget = 225 * 1024;
+  const size_t fixed = 2 * red_floats<NT>() * sizeof(float) + 256;
+  int stages = (int)((budget - fixed) / stage_bytes<NT>());
+  if (stages > 8) stages = 8;
+  p.stages = stages;
+  const size_t smem = (size_t)stages * stage_bytes<NT>() + fixed;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(stream_kernel<NT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int KB = p.k / 128;
+  CUtensorMap tm_w, tm_x, tm_xs;
+  if (!make_map(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT32, p.w, (uint64_t)p.k / 4, (uint64_t)w_rows, (uint64_t)p.k,
+                kChunk / 4, 16) ||
+      !make_map(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT32, p.x, (uint64_t)p.groups * p.k / 4, (uint64_t)p.rows,
+                (uint64_t)p.groups * p.k, kChunk / 4, NT * 8) ||
+      !make_map(&tm_xs, CU_TENSOR_MAP_DATA_TYPE_UINT32, p.xs, (uint64_t)p.groups * KB, (uint64_t)p.rows,
+                (uint64_t)p.groups * KB * 4, 8, NT * 8))
+    return cudaErrorInvalidValue;
+  stream_kernel<NT, MODE><<<grid, kThreads, smem, s>>>(p, tm_w, tm_x, tm_xs);
+  return cudaGetLastError();
+}
+
+template <int MODE>
+static cudaError_t launch_stream(const StreamP& p, int grid, long long w_rows, cudaStream_t s) {
+  if (p.rows <= 8) return launch_stream_nt<1, MODE>(p, grid, w_rows, s);
+  if (p.rows <= 16) return launch_stream_nt<2, MODE>(p, grid, w_rows, s);
+  return launch_stream_nt<4, MODE>(p, grid, w_rows, s);
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+cudaError_t launch_moe_up_stream(const B200MoeUpArgs& a, uint32_t* status, cudaStream_t s) {
+  StreamP p{};
+  p.w = (const uint8_t*)a.w13;
+  p.ws = a.w13_scale;
+  p.x = (const uint8_t*)a.xq;
+  p.xs = a.x_scale;
+  p.y = a.mid;
+  p.rows = a.rows;
+  p.n = a.inter;
+  p.k = a.hidden;
+  p.groups = 1;
+  p.ldy = a.inter;
+  p.inter = a.inter;
+  p.tiles = a.inter / 16;
+  p.union_count = a.union_count;
+  p.union_ids = a.union_ids;
+  p.w_stride_e = 2ll * a.inter * a.hidden;
+  p.ws_stride_e = (long long)((2 * a.inter + 127) / 128) * (a.hidden / 128);
+  p.y_stride_u = (long long)a.rows * a.inter * 2;
+  p.limit = a.swiglu_limit;
+  p.status = status;
+  return launch_stream<MODE_SWIGLU>(p, sm_count(), (long long)(a.experts + 1) * 2 * a.inter, s);
+}
+
+cudaError_t launch_gemv_stream(const B200GemvFp8Args& a, uint32_t* status, cudaStream_t s) {
+  StreamP p{};
+  p.w = (const uint8_t*)a.w;
+  p.ws = a.w_scale;
+  p.x = (const uint8_t*)a.xq;
+  p.xs = a.x_scale;
+  p.y = a.y;
+  p.rows = a.rows;
+  p.n = a.n;
+  p.k = a.k;
+  p.groups = a.groups;
+  p.ldy = a.ldy;
+  p.y_f32 = a.y_f32;
+  p.tiles = (a.n + 31) / 32;
+  p.status = status;
+  int grid = sm_count();
+  if (p.tiles < grid) grid = p.tiles;
+  return launch_stream<MODE_PLAIN>(p, grid, a.n, s);
+}
+
+}  // namespace b200mono

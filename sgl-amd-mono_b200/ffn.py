@@ -107,3 +107,46 @@ class FfnRunner:
         s = stream or torch.cuda.current_stream(self.device)
         self.lib.call("moe_ffn", a, s.cuda_stream)
         return out
+
+    def stage_calls(self, x, out, residual=None, add_residual=False):
+        """The launch sequence of :meth:`ffn` as separate C-ABI calls, [(entry point, args struct)] in
+        order, over the same scratch regions: for per-kernel timing and stage-by-stage checks."""
+        b = self.build
+        rows = x.shape[0]
+        L = cabi.STRUCTS["B200MoeFfnLayout"]()
+        self.lib.call("moe_ffn_layout", rows, b.hidden, b.inter, b.experts, b.topk, L)
+        self.step_layout = L
+        sc = self.scratch
+
+        def at(name):
+            return sc[getattr(L, name):]
+
+        res = None
+        if add_residual:
+            res = at("res") if residual is not None else x
+        return [
+            ("norm_quant", cabi.fill("B200NormQuantArgs", x=x, residual=residual, weight=self.w.norm, res_out=at("res"),
+                                     y=at("xn"), q=at("xq"), q_scale=at("xs"), rows=rows, hidden=b.hidden, eps=b.eps,
+                                     gemma=0)),
+            ("router", cabi.fill("B200RouterArgs", x=at("xn"), gate_w=self.w.gate_w, bias=self.w.bias,
+                                 logit_parts=at("logit_parts"), logits=at("logits"), topk_ids=at("topk_ids"),
+                                 topk_w=at("topk_w"), union_count=at("union_count"), union_ids=at("union_ids"),
+                                 union_pick=at("union_pick"), counter=at("counter"), rows=rows, hidden=b.hidden,
+                                 experts=b.experts, topk=b.topk, score_fn=b.score_fn, route_scale=b.route_scale,
+                                 has_shared=int(b.has_shared))),
+            ("moe_up", cabi.fill("B200MoeUpArgs", xq=at("xq"), x_scale=at("xs"), w13=self.w.w13, w13_scale=self.w.w13_s,
+                                 union_count=at("union_count"), union_ids=at("union_ids"), mid=at("mid"), rows=rows,
+                                 hidden=b.hidden, inter=b.inter, experts=b.experts, union_cap=L.union_cap,
+                                 swiglu_limit=b.swiglu_limit, status=at("status"), variant=0)),
+            ("quant128", cabi.fill("B200Quant128Args", x=at("mid"), q=at("midq"), q_scale=at("mids"),
+                                   rows=L.union_cap * rows, cols=b.inter, zero_rule=0)),
+            ("moe_down", cabi.fill("B200MoeDownArgs", midq=at("midq"), mid_scale=at("mids"), w2=self.w.w2,
+                                   w2_scale=self.w.w2_s, union_count=at("union_count"), union_ids=at("union_ids"),
+                                   union_pick=at("union_pick"), topk_w=at("topk_w"), residual=res, out=out, rows=rows,
+                                   hidden=b.hidden, inter=b.inter, experts=b.experts, topk=b.topk)),
+        ]
+
+    def status(self) -> int:
+        """The launch's device status word (0 = clean); synchronises."""
+        L = self.step_layout
+        return int(self.scratch[L.status : L.status + 4].view(torch.int32).item())

@@ -58,7 +58,7 @@ def test_null_and_shape_rejection(lib):
         lib.call("gemv_fp8", cabi.fill("B200GemvFp8Args", w=272, w_scale=256, xq=256, x_scale=256, y=256,
                                        rows=1, n=16, k=128, groups=1, ldy=16), None)
     with pytest.raises(cabi.B200MonoError, match="score_fn"):
-        lib.call("router", cabi.fill("B200RouterArgs", x=256, gate_w=256, logits=256, topk_ids=256, topk_w=256,
+        lib.call("router", cabi.fill("B200RouterArgs", x=256, gate_w=256, logit_parts=256, logits=256, topk_ids=256, topk_w=256,
                                      union_count=256, union_ids=256, union_pick=256, counter=256, rows=1,
                                      hidden=128, experts=8, topk=2, score_fn=2), None)
     with pytest.raises(cabi.B200MonoError) as e:

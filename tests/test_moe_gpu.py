@@ -84,6 +84,8 @@ GEMV_CASES = [
     (17, 256, 256, 1),    # two MMA column groups, ragged
     (32, 512, 384, 1),    # four column groups, k blocks not divisible by the slices
     (5, 16, 128, 1),      # one tile, one k block
+    (8, 48, 1024, 1),     # ring: last unit has one row set only
+    (3, 2240, 1536, 1),   # ring: second stage half full
 ]
 
 
@@ -95,17 +97,24 @@ def test_gemv_fp8_against_oracle(lib, rows, n, k, groups):
     xq, xs = Q.quant128(x)
     ref = Q.gemv_fp8(xq, xs, wq, ws, groups)
     d = [t.to(DEV) for t in (wq, ws, xq, xs)]
-    for f32 in (1, 0):
-        y = torch.full((rows, n + 16), float("nan"), dtype=torch.float32 if f32 else torch.bfloat16, device=DEV)
-        lib.call("gemv_fp8", cabi.fill("B200GemvFp8Args", w=d[0], w_scale=d[1], xq=d[2], x_scale=d[3], y=y, rows=rows,
-                                       n=n, k=k, groups=groups, ldy=n + 16, y_f32=f32), stream())
-        torch.cuda.synchronize()
-        assert torch.isnan(y[:, n:].float()).all(), "wrote past n"
-        got = y[:, :n].float().cpu()
-        if f32:
-            assert rel(got, ref) < 2e-6, rel(got, ref)  # only the f32 summation order differs
-        else:
-            assert torch.equal(got, got.bfloat16().float()) and rel(got, ref) < 5e-3
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ring_ok = k % 512 == 0 and (groups == 1 or (n // groups) % 32 == 0)
+    for variant in (1, 2) if ring_ok else (1,):
+        for f32 in (1, 0):
+            y = torch.full((rows, n + 16), float("nan"), dtype=torch.float32 if f32 else torch.bfloat16, device=DEV)
+            lib.call("gemv_fp8", cabi.fill("B200GemvFp8Args", w=d[0], w_scale=d[1], xq=d[2], x_scale=d[3], y=y,
+                                           rows=rows, n=n, k=k, groups=groups, ldy=n + 16, y_f32=f32, status=status,
+                                           variant=variant), stream())
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0, hex(int(status.item()))
+            assert torch.isnan(y[:, n:].float()).all(), "wrote past n"
+            got = y[:, :n].float().cpu()
+            if f32:
+                e = rel(got, ref)
+                print(f"gemv rows={rows} n={n} k={k} groups={groups} variant={variant}: f32 rel {e:.2e}")
+                assert e < 1e-4, e  # only the f32 summation order (and the MMA's in-block accumulation) differs
+            else:
+                assert torch.equal(got, got.bfloat16().float()) and rel(got, ref) < 5e-3
 
 
 # ------------------------------------------------------------------ router
@@ -124,6 +133,7 @@ def test_router_bit_exact(lib, rows, hidden, experts, topk, score_fn, shared):
     if rows > 1:
         gw[7] = gw[3]  # identical experts: a tie the lower id must win
     logits = torch.full((rows, experts), float("nan"), device=DEV)
+    parts = torch.full((rows, experts, -(-hidden // 1024)), float("nan"), device=DEV)
     ids = torch.full((rows, topk), -1, dtype=torch.int32, device=DEV)
     wts = torch.full((rows, topk), float("nan"), device=DEV)
     ucount = torch.zeros(1, dtype=torch.int32, device=DEV)
@@ -132,7 +142,7 @@ def test_router_bit_exact(lib, rows, hidden, experts, topk, score_fn, shared):
     counter = torch.zeros(1, dtype=torch.int32, device=DEV)
     xd, gd = x.to(DEV), gw.to(DEV)
     bd = None if bias is None else bias.to(DEV)
-    args = cabi.fill("B200RouterArgs", x=xd, gate_w=gd, bias=bd, logits=logits, topk_ids=ids, topk_w=wts,
+    args = cabi.fill("B200RouterArgs", x=xd, gate_w=gd, bias=bd, logit_parts=parts, logits=logits, topk_ids=ids, topk_w=wts,
                      union_count=ucount, union_ids=uids, union_pick=pick, counter=counter, rows=rows, hidden=hidden,
                      experts=experts, topk=topk, score_fn=score_fn, route_scale=2.5, has_shared=int(shared))
     for _ in range(2):  # the arrival counter must reset itself
@@ -202,6 +212,7 @@ def _check_block(cfg, w, x, residual=None, add_residual=False, width=None):
     assert torch.equal(reg("midq", torch.uint8, (L.union_cap, rows, I))[:U].reshape(U * rows, I), u8(mq))
     assert torch.equal(reg("mids", torch.float32, (L.union_cap, rows, I // 128))[:U].reshape(U * rows, -1), ms)
     assert not torch.isnan(out.float()).any()
+    assert int(reg("status", torch.int32, (1,)).item()) == 0
     e = rel(out, o["out"])
     assert e < 2e-2, e  # bf16 hidden after FP8 quant
     return out, o, e
