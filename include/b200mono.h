@@ -229,6 +229,27 @@ typedef struct {
 } B200MoeFfnArgs;
 int b200mono_moe_ffn(const B200MoeFfnArgs* a, void* stream);
 
+/* ------------------------------------------------------------------------
+ * The same block for callers that cannot allocate device memory.  This entry
+ * point has no counterpart in the reference (its runner always owns a scratch
+ * tensor); it exists for hosts that cannot supply one: a serving process whose
+ * KV-cache pool has already taken all free HBM, so that a cudaMalloc at step
+ * time may fail, or a bare FFI binding that holds input/output pointers and
+ * has no allocator.  The intermediates live in a fixed array inside the
+ * library image (B200MONO_STATIC_SCRATCH_BYTES on every GPU that loads the
+ * library, until the process exits); the call allocates and frees nothing.
+ *   - a->scratch must be NULL and a->scratch_bytes 0; all other fields as above.
+ *   - Problems whose b200mono_moe_ffn_layout().total exceeds the array are
+ *     refused with B200MONO_E_SCRATCH and a message naming both sizes.
+ *   - The first call on a device resolves the array's device address; make
+ *     that call outside any stream capture.
+ *   - All calls on a device share the array, which keeps the previous call's
+ *     contents; the words that must start at zero are cleared on `stream`
+ *     first.  Calls that can overlap on the GPU race: serialise them.
+ */
+#define B200MONO_STATIC_SCRATCH_BYTES 8388608
+int b200mono_moe_ffn_static(const B200MoeFfnArgs* a, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -18,6 +18,8 @@ static int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+
 static int cuda_status(cudaError_t e, const char* what) {
   if (e == cudaSuccess) return B200MONO_OK;
   snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));

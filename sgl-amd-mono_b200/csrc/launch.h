@@ -19,6 +19,9 @@ cudaError_t launch_moe_down(const B200MoeDownArgs& a, cudaStream_t s);
 cudaError_t launch_moe_up_stream(const B200MoeUpArgs& a, uint32_t* status, cudaStream_t s);
 cudaError_t launch_gemv_stream(const B200GemvFp8Args& a, uint32_t* status, cudaStream_t s);
 
+// records `msg` as the calling thread's last error (what b200mono_last_error() returns)
+void set_last_error(const char* msg);
+
 // upper bound of distinct experts a step can pick (+1 shared)
 inline int union_capacity(int rows, int topk, int experts, int has_shared) {
   int u = rows * topk < experts ? rows * topk : experts;

@@ -1,0 +1,75 @@
+"""The entry point for callers that cannot allocate device memory.
+
+`b200mono_moe_ffn_static` runs the MoE FFN block with its intermediates in a fixed array that
+lives inside the library image, for hosts that cannot hand over a scratch buffer: a serving
+process whose KV-cache pool already owns all free HBM (a cudaMalloc at step time may fail) or
+a bare FFI binding that has input/output pointers and no allocator.  The kernels are the
+same as `b200mono_moe_ffn`'s, so for the same inputs the outputs must be bit-identical
+(tolerance 0, as for the replay checks elsewhere in this suite).  Two calls in a row share
+the array; the second must not see anything the first left behind.
+
+This file sorts last on purpose: a run that stops at the first failure has then already run
+every other test.  It also passes alone in a fresh process (the first call on a device
+resolves the array's address).
+"""
+
+import pytest
+import torch
+
+import sgl_amd_mono_b200  # noqa: F401
+from oracle import inputs
+from sgl_amd_mono_b200 import cabi
+
+
+def _args(cfg, w, x, out, res, scratch=None):
+    return cabi.fill(
+        "B200MoeFfnArgs", x=x, residual=res, out=out, norm_w=w["norm"], gate_w=w["gate_w"], gate_bias=w["bias"],
+        w13=w["w13"], w13_scale=w["w13_s"], w2=w["w2"], w2_scale=w["w2_s"], scratch=scratch,
+        scratch_bytes=0 if scratch is None else scratch.numel(), rows=x.shape[0], hidden=cfg["hidden"],
+        inter=cfg["inter"], experts=cfg["experts"], topk=cfg["topk"], score_fn=cfg["score_fn"],
+        has_shared=int(cfg["has_shared"]), add_residual=1, eps=cfg["eps"], route_scale=cfg["route_scale"],
+        swiglu_limit=cfg["swiglu_limit"])
+
+
+def test_static_entry_refuses_what_does_not_fit(lib):
+    # rows=32 of the TP1 layer needs far more than the built-in array; refused before any CUDA work
+    a = cabi.fill("B200MoeFfnArgs", x=256, out=256, norm_w=256, gate_w=256, w13=256, w13_scale=256, w2=256,
+                  w2_scale=256, rows=32, hidden=7168, inter=2048, experts=256, topk=8)
+    with pytest.raises(cabi.B200MonoError) as e:
+        lib.call("moe_ffn_static", a, None)
+    assert e.value.code == cabi.ENUMS["B200MONO_E_SCRATCH"]
+    assert str(cabi.ENUMS["B200MONO_STATIC_SCRATCH_BYTES"]) in str(e.value) and "needs" in str(e.value)
+    a.scratch, a.scratch_bytes, a.rows = 256, 1024, 4
+    with pytest.raises(cabi.B200MonoError, match="must be zero"):
+        lib.call("moe_ffn_static", a, None)
+
+
+@pytest.mark.gpu
+def test_static_entry_matches_the_scratch_entry_twice_in_a_row(lib):
+    dev = "cuda"
+    cfg = inputs.C1
+    w = inputs.moe_weights(cfg, seed=4, device=dev)
+    L = cabi.STRUCTS["B200MoeFfnLayout"]()
+    lib.call("moe_ffn_layout", 8, cfg["hidden"], cfg["inter"], cfg["experts"], cfg["topk"], L)
+    assert L.total <= cabi.ENUMS["B200MONO_STATIC_SCRATCH_BYTES"]
+    scratch = torch.zeros(L.total, dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    calls = []
+    for i, rows in enumerate((8, 3)):  # the second call is narrower: stale rows of the first must not leak
+        x = inputs.rows_bf16(rows, cfg["hidden"], seed=60 + i).to(dev)
+        res = inputs.rows_bf16(rows, cfg["hidden"], seed=70 + i).to(dev)
+        calls.append((x, res))
+    want = []
+    for x, res in calls:
+        out = torch.full_like(x, float("nan"))
+        lib.call("moe_ffn", _args(cfg, w, x, out, res, scratch), stream)
+        want.append(out)
+    got = []
+    for x, res in calls:  # two calls in a row on the shared array, no synchronisation in between
+        out = torch.full_like(x, float("nan"))
+        lib.call("moe_ffn_static", _args(cfg, w, x, out, res), stream)
+        got.append(out)
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        assert not torch.isnan(a.float()).any()
+        assert torch.equal(a, b)
