@@ -177,7 +177,7 @@ def run_ours(args):
             with torch.cuda.graph(gr, stream=stream):
                 layers[i % args.layers].ffn(xs[i % n_in], out, res, True)
             graphs.append(gr)
-    launches_per_step = 5
+    launches_per_step = 6
 
     def barrier():
         if world > 1:

@@ -51,6 +51,12 @@ const char* b200mono_last_error(void);
 int b200mono_device_ok(void);
 /* Number of SMs of the current device (persistent grids are sized from it). */
 int b200mono_sm_count(void);
+/* Timeline marks (the counterpart of the reference's SGLANG_AMD_MONO_TIMELINE stamps,
+ * sgl_amd_mono/common/stamps.py:15-33): with a non-NULL device buffer of 4*256*8 u64 the
+ * persistent kernels store %globaltimer at their pipeline events for the first 4 CTAs and
+ * 256 stages: [cta][stage][0 producer got a free stage, 1 copies issued, 2 consumer starts
+ * waiting, 3 stage arrived, 4 stage released, 5 epilogue done].  NULL switches it off. */
+int b200mono_set_timeline(void* device_buffer);
 /* sizeof() of every argument struct below, in declaration order; returns how many
  * there are.  A binding checks its own layouts against these at load time. */
 int b200mono_abi_sizes(int32_t* out, int32_t capacity);
@@ -189,6 +195,11 @@ typedef struct {
   const void* residual;     /* bf16 [rows, hidden] or NULL: added in f32 before the final rounding */
   void* out;                /* bf16 [rows, hidden] */
   int32_t rows, hidden, inter, experts, topk;
+  int32_t has_shared;       /* 1: the last union entry is the shared expert (slot topk) */
+  void* contrib;            /* bf16 [topk+1, rows, hidden] scratch or NULL; needed by the persistent kernel */
+  uint32_t* status;         /* u32 [1] or NULL: as in B200GemvFp8Args */
+  int32_t union_cap;        /* entries of midq / mid_scale (their first dimension) */
+  int32_t variant;          /* 0: pick automatically; 1: one CTA per 16 rows; 2: persistent TMA-ring kernel */
 } B200MoeDownArgs;
 int b200mono_moe_down(const B200MoeDownArgs* a, void* stream);
 
@@ -202,7 +213,7 @@ int b200mono_moe_down(const B200MoeDownArgs* a, void* stream);
  */
 typedef struct {
   int64_t status, res, xn, xq, xs, logit_parts, logits, topk_ids, topk_w, union_count, union_ids, union_pick, counter,
-      mid, midq, mids, total;
+      mid, midq, mids, contrib, total;
   int32_t union_cap, pad_;
 } B200MoeFfnLayout;
 int b200mono_moe_ffn_layout(int32_t rows, int32_t hidden, int32_t inter, int32_t experts,
@@ -228,6 +239,44 @@ typedef struct {
   float eps, route_scale, swiglu_limit;
 } B200MoeFfnArgs;
 int b200mono_moe_ffn(const B200MoeFfnArgs* a, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Tensor-parallel all-reduce inside a kernel, over NVLink peer memory, with the
+ * residual add fused: out = bf16(sum over ranks in rank order (f32) + residual).
+ * Replaces peer_reduce (sgl_amd_mono/glm53/gfx950/kernel.py:2035-2092),
+ * seam.stage_push/stage_reduce (sgl_amd_mono/deepseek_v41/gfx950/stages/seam.py:388-431)
+ * and down_combine/stage_reduce (sgl_amd_mono/deepseek_v41/gfx950/stages/moe.py:1157-1276);
+ * the buffer exchange replaces PeerBuffer (sgl_amd_mono/common/peer.py:122-166).
+ * Every rank pushes (two bf16, tag) words into all inboxes and sums its own inbox;
+ * all ranks end with identical bits.  `words` lives in this rank's memory:
+ * [0] epoch (advanced by the kernel, so a captured graph replays with fresh tags),
+ * [1] arrival counter, [2] status (0, or 5<<16 | rank it gave up waiting for).
+ * With slots > 0 `partial` is the MoE down stage's [slots, rows, hidden] buffer and the
+ * slot-ordered bf16 sum is taken while pushing.
+ * phase: 0 or 3 = push and reduce; 1 = push only; 2 = reduce only (1 and 2 let a test
+ * emulate several ranks with consecutive launches on one GPU).
+ */
+typedef struct {
+  const void* partial;   /* bf16 [rows, hidden], or [slots, rows, hidden] when slots > 0 */
+  const void* residual;  /* bf16 [rows, hidden] or NULL */
+  void* out;             /* bf16 [rows, hidden] */
+  const void* peers;     /* device array of tp pointers: every rank's inbox as mapped in this process */
+  uint32_t* words;       /* u32 [4], zero before the first launch */
+  int32_t rows, hidden, tp, rank;
+  int32_t max_rows;      /* rows the inboxes were sized for */
+  int32_t slots, phase;
+  int32_t timeout_ms;    /* deadline of the wait for peers; 0 = 2000 */
+} B200AllReduceArgs;
+int b200mono_allreduce(const B200AllReduceArgs* a, void* stream);
+/* Bytes of one rank's inbox: 2 parities x tp sources x max_rows x hidden/4 messages of 16 bytes. */
+int b200mono_allreduce_inbox_bytes(int32_t tp, int32_t max_rows, int32_t hidden, int64_t* out);
+/* Setup-time helpers (they allocate and synchronise): zero-filled device buffer that can be
+ * shared with the other ranks of the node; 64-byte IPC handle of it; mapping of a peer's. */
+int b200mono_peer_alloc(int64_t bytes, void** out);
+int b200mono_peer_free(void* p);
+int b200mono_peer_export(void* p, void* handle64);
+int b200mono_peer_import(const void* handle64, void** out);
+int b200mono_peer_unmap(void* p);
 
 /* ------------------------------------------------------------------------
  * The same block for callers that cannot allocate device memory.  This entry

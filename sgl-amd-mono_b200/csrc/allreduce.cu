@@ -1,0 +1,145 @@
+// In-kernel tensor-parallel all-reduce over NVLink peer memory, residual add fused.
+//
+// One-shot push: every rank stores its bf16 partial rows into the inbox of every rank
+// (its own included) and then sums the tp inboxes of its own memory in rank order in f32,
+// adds the residual and rounds once to bf16, so every rank ends with the same bits.  A
+// message word is 8 bytes: (two bf16 values, tag); the tag is the launch's epoch, so a
+// word is valid exactly when its tag matches and no flag, fence or store drain is needed
+// (8-byte aligned stores are single-copy atomic).  Two words travel per 16-byte store.
+// Inboxes are double-buffered by epoch parity; launch n+2 may reuse the half of launch n
+// because every launch contains an exchange in which each rank waits for every other.
+// Polls read the rank's own memory only (never across NVLink) and give up after a
+// deadline: the kernel then records (site, rank it was waiting for) in the status word,
+// writes zeros for what it could not sum and returns; the host discards the step.
+//
+// The partial can also be given as the MoE down stage's per-slot contributions
+// [slots][rows][hidden]: the push then performs the slot-ordered bf16 sum first, which
+// fuses the routed-expert combine into the exchange.
+#include "common.cuh"
+#include "launch.h"
+
+namespace b200mono {
+
+struct ArP {
+  const __nv_bfloat16* partial;  // [rows, hidden] or [slots, rows, hidden]
+  const __nv_bfloat16* residual;
+  __nv_bfloat16* out;
+  void* const* peers;   // device array [tp]: inbox base of every rank, in this rank's address space
+  uint32_t* words;      // [0] epoch, [1] arrival counter, [2] status
+  int rows, hidden, tp, rank, max_rows, slots, phase;
+  unsigned long long timeout_ns;
+};
+
+// chunk = 4 consecutive bf16 values of one row = one 16-byte message
+__device__ __forceinline__ size_t inbox_chunk(const ArP& p, int parity, int src, size_t chunk) {
+  const size_t per_src = (size_t)p.max_rows * (p.hidden >> 2);
+  return ((size_t)parity * p.tp + src) * per_src + chunk;
+}
+
+__global__ __launch_bounds__(256) void allreduce_kernel(ArP p) {
+  const uint32_t epoch = ld_relaxed_gpu_u32(p.words);
+  const uint32_t tag = epoch + 1;
+  const int parity = (int)(epoch & 1u);
+  const size_t nchunk = (size_t)p.rows * (p.hidden >> 2);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+
+  if (p.phase & 1) {
+    for (size_t c = first; c < nchunk; c += stride) {
+      uint2 v;
+      if (p.slots > 0) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int sl = 0; sl < p.slots; ++sl) {
+          const uint2 q = reinterpret_cast<const uint2*>(p.partial + (size_t)sl * p.rows * p.hidden)[c];
+          s[0] = round_bf16(__fadd_rn(s[0], bf16_lo(q.x)));
+          s[1] = round_bf16(__fadd_rn(s[1], bf16_hi(q.x)));
+          s[2] = round_bf16(__fadd_rn(s[2], bf16_lo(q.y)));
+          s[3] = round_bf16(__fadd_rn(s[3], bf16_hi(q.y)));
+        }
+        v.x = pack_bf16x2(s[0], s[1]);
+        v.y = pack_bf16x2(s[2], s[3]);
+      } else {
+        v = reinterpret_cast<const uint2*>(p.partial)[c];
+      }
+      const uint4 msg = make_uint4(v.x, tag, v.y, tag);
+      const size_t at = inbox_chunk(p, parity, p.rank, c);
+      for (int d = 0; d < p.tp; ++d) {
+        const int dst = (p.rank + 1 + d) % p.tp;  // start with the neighbour: spreads the links
+        st_relaxed_sys_u4(reinterpret_cast<uint4*>(p.peers[dst]) + at, msg);
+      }
+    }
+  }
+
+  if (p.phase & 2) {
+    const uint4* inbox = reinterpret_cast<const uint4*>(p.peers[p.rank]);
+    const unsigned long long t0 = globaltimer_ns();
+    bool gave_up = false;
+    for (size_t c = first; c < nchunk; c += stride) {
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int src = 0; src < p.tp; ++src) {
+        const uint4* w = inbox + inbox_chunk(p, parity, src, c);
+        uint4 m = ld_relaxed_sys_u4(w);
+        uint32_t spin = 0;
+        while ((m.y != tag || m.w != tag) && !gave_up) {
+          if ((++spin & 255u) == 0 && globaltimer_ns() - t0 > p.timeout_ns) {
+            gave_up = true;
+            atomicCAS(p.words + 2, 0u, (5u << 16) | (uint32_t)src);
+            break;
+          }
+          m = ld_relaxed_sys_u4(w);
+        }
+        if (gave_up) m = make_uint4(0, 0, 0, 0);
+        s[0] = __fadd_rn(s[0], bf16_lo(m.x));
+        s[1] = __fadd_rn(s[1], bf16_hi(m.x));
+        s[2] = __fadd_rn(s[2], bf16_lo(m.z));
+        s[3] = __fadd_rn(s[3], bf16_hi(m.z));
+      }
+      if (p.residual) {
+        const uint2 r = reinterpret_cast<const uint2*>(p.residual)[c];
+        s[0] = __fadd_rn(s[0], bf16_lo(r.x));
+        s[1] = __fadd_rn(s[1], bf16_hi(r.x));
+        s[2] = __fadd_rn(s[2], bf16_lo(r.y));
+        s[3] = __fadd_rn(s[3], bf16_hi(r.y));
+      }
+      reinterpret_cast<uint2*>(p.out)[c] = make_uint2(pack_bf16x2(s[0], s[1]), pack_bf16x2(s[2], s[3]));
+    }
+    // the CTA that arrives last advances the epoch (everyone has read it by then)
+    __shared__ int s_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      s_last = atomicAdd(p.words + 1, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+      p.words[1] = 0;
+      __threadfence();
+      p.words[0] = epoch + 1;
+    }
+  }
+}
+
+cudaError_t launch_allreduce(const B200AllReduceArgs& a, cudaStream_t s) {
+  ArP p{};
+  p.partial = (const __nv_bfloat16*)a.partial;
+  p.residual = (const __nv_bfloat16*)a.residual;
+  p.out = (__nv_bfloat16*)a.out;
+  p.peers = (void* const*)a.peers;
+  p.words = a.words;
+  p.rows = a.rows;
+  p.hidden = a.hidden;
+  p.tp = a.tp;
+  p.rank = a.rank;
+  p.max_rows = a.max_rows;
+  p.slots = a.slots;
+  p.phase = a.phase ? a.phase : 3;
+  p.timeout_ns = a.timeout_ms > 0 ? (unsigned long long)a.timeout_ms * 1000000ull : 2000000000ull;
+  const size_t nchunk = (size_t)a.rows * (a.hidden / 4);
+  int grid = (int)((nchunk + 255) / 256);
+  if (grid > 128) grid = 128;  // all CTAs must be resident: a CTA waits for peers while holding its SM
+  if (grid < 1) grid = 1;
+  allreduce_kernel<<<grid, 256, 0, s>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace b200mono

@@ -18,6 +18,9 @@ static int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+static void* g_timeline = nullptr;
+void* timeline_buffer() { return g_timeline; }
+
 void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
 
 static int cuda_status(cudaError_t e, const char* what) {
@@ -55,10 +58,16 @@ int b200mono_abi_sizes(int32_t* out, int32_t capacity) {
   const int32_t sizes[] = {(int32_t)sizeof(B200NormQuantArgs), (int32_t)sizeof(B200Quant128Args),
                            (int32_t)sizeof(B200GemvFp8Args),   (int32_t)sizeof(B200RouterArgs),
                            (int32_t)sizeof(B200MoeUpArgs),     (int32_t)sizeof(B200MoeDownArgs),
-                           (int32_t)sizeof(B200MoeFfnLayout),  (int32_t)sizeof(B200MoeFfnArgs)};
+                           (int32_t)sizeof(B200MoeFfnLayout),  (int32_t)sizeof(B200MoeFfnArgs),
+                           (int32_t)sizeof(B200AllReduceArgs)};
   const int32_t n = (int32_t)(sizeof(sizes) / sizeof(sizes[0]));
   for (int32_t i = 0; i < n && i < capacity; ++i) out[i] = sizes[i];
   return n;
+}
+
+int b200mono_set_timeline(void* device_buffer) {
+  g_timeline = device_buffer;
+  return B200MONO_OK;
 }
 
 int b200mono_sm_count(void) {
@@ -159,6 +168,13 @@ int b200mono_moe_down(const B200MoeDownArgs* a, void* stream) {
   if (int rc = check_moe_dims("moe_down", a->rows, a->hidden, a->inter, a->experts)) return rc;
   REQUIRE(a->topk >= 1 && a->topk <= 16, "moe_down: topk=%d outside 1..16", a->topk);
   REQUIRE(aligned(a->midq, 16) && aligned(a->w2, 32), "moe_down: w2 must be 32-byte and midq 16-byte aligned");
+  REQUIRE(a->variant >= 0 && a->variant <= 2, "moe_down: variant=%d outside 0..2", a->variant);
+  const bool ring_ok = a->contrib && a->union_cap >= 1 && down_stream_ok(*a) && aligned(a->contrib, 16) &&
+                       aligned(a->out, 16) && (!a->residual || aligned(a->residual, 16));
+  REQUIRE(a->variant != 2 || ring_ok, "moe_down: variant=2 not available for this shape (rows <= 8, inter %% 256 == 0, contrib given)");
+  if (a->variant != 1 && ring_ok)
+    return cuda_status(launch_moe_down_stream(*a, a->contrib, a->status, a->has_shared, a->union_cap, (cudaStream_t)stream),
+                       "moe_down(ring)");
   return cuda_status(launch_moe_down(*a, (cudaStream_t)stream), "moe_down");
 }
 
@@ -192,6 +208,7 @@ int b200mono_moe_ffn_layout(int32_t rows, int32_t hidden, int32_t inter, int32_t
   out->mid = take((int64_t)cap * rows * inter * 2);
   out->midq = take((int64_t)cap * rows * inter);
   out->mids = take((int64_t)cap * rows * (inter / 128) * 4);
+  out->contrib = take((int64_t)(topk + 1) * rows * hidden * 2);
   out->total = at;
   out->union_cap = cap;
   out->pad_ = 0;
@@ -290,6 +307,11 @@ int b200mono_moe_ffn(const B200MoeFfnArgs* a, void* stream) {
   dn.inter = a->inter;
   dn.experts = a->experts;
   dn.topk = a->topk;
+  dn.has_shared = a->has_shared;
+  dn.contrib = sc + L.contrib;
+  dn.status = (uint32_t*)(sc + L.status);
+  dn.union_cap = L.union_cap;
+  dn.variant = 0;
   return b200mono_moe_down(&dn, s);
 }
 

@@ -19,6 +19,16 @@ cudaError_t launch_moe_down(const B200MoeDownArgs& a, cudaStream_t s);
 cudaError_t launch_moe_up_stream(const B200MoeUpArgs& a, uint32_t* status, cudaStream_t s);
 cudaError_t launch_gemv_stream(const B200GemvFp8Args& a, uint32_t* status, cudaStream_t s);
 
+// persistent down projection + slot-ordered combine (rows <= 8, inter a multiple of 256 up to 2048)
+bool down_stream_ok(const B200MoeDownArgs& a);
+cudaError_t launch_moe_down_stream(const B200MoeDownArgs& a, void* contrib, uint32_t* status, int has_shared,
+                                   int union_cap, cudaStream_t s);
+
+cudaError_t launch_allreduce(const B200AllReduceArgs& a, cudaStream_t s);
+
+// device buffer for timeline marks (null: tracing off), set by b200mono_set_timeline
+void* timeline_buffer();
+
 // records `msg` as the calling thread's last error (what b200mono_last_error() returns)
 void set_last_error(const char* msg);
 

@@ -1,0 +1,100 @@
+// Symmetric peer memory for the in-kernel all-reduce: plain cudaMalloc'd buffers shared
+// between the ranks of one node through CUDA IPC handles.  Setup-time only (these calls
+// allocate and synchronise; nothing here runs on the step path).
+#include <stdio.h>
+#include <string.h>
+
+#include "launch.h"
+
+using namespace b200mono;
+
+static int peer_fail(cudaError_t e, const char* what) {
+  char msg[256];
+  snprintf(msg, sizeof(msg), "%s: %s", what, cudaGetErrorString(e));
+  set_last_error(msg);
+  return (int)e;
+}
+
+extern "C" {
+
+int b200mono_allreduce_inbox_bytes(int32_t tp, int32_t max_rows, int32_t hidden, int64_t* out) {
+  if (!out || tp < 1 || tp > 16 || max_rows < 1 || hidden < 4 || hidden % 4) {
+    set_last_error("allreduce_inbox_bytes: tp in 1..16, max_rows >= 1, hidden a multiple of 4");
+    return B200MONO_E_ARG;
+  }
+  // [2 parities][tp sources][max_rows * hidden / 4 messages of 16 bytes]
+  *out = 2ll * tp * max_rows * (hidden / 4) * 16;
+  return B200MONO_OK;
+}
+
+int b200mono_peer_alloc(int64_t bytes, void** out) {
+  if (!out || bytes <= 0) {
+    set_last_error("peer_alloc: bytes must be positive");
+    return B200MONO_E_ARG;
+  }
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+  if (e != cudaSuccess) return peer_fail(e, "peer_alloc: cudaMalloc");
+  e = cudaMemset(p, 0, (size_t)bytes);  // tag 0 is never a valid epoch tag
+  if (e != cudaSuccess) return peer_fail(e, "peer_alloc: cudaMemset");
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return peer_fail(e, "peer_alloc: cudaDeviceSynchronize");
+  *out = p;
+  return B200MONO_OK;
+}
+
+int b200mono_peer_free(void* p) {
+  cudaError_t e = cudaFree(p);
+  return e == cudaSuccess ? B200MONO_OK : peer_fail(e, "peer_free");
+}
+
+int b200mono_peer_export(void* p, void* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (!p || !handle64) {
+    set_last_error("peer_export: null pointer");
+    return B200MONO_E_ARG;
+  }
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return peer_fail(e, "peer_export: cudaIpcGetMemHandle");
+  memcpy(handle64, &h, 64);
+  return B200MONO_OK;
+}
+
+int b200mono_peer_import(const void* handle64, void** out) {
+  if (!handle64 || !out) {
+    set_last_error("peer_import: null pointer");
+    return B200MONO_E_ARG;
+  }
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return peer_fail(e, "peer_import: cudaIpcOpenMemHandle (is peer access available between the GPUs?)");
+  *out = p;
+  return B200MONO_OK;
+}
+
+int b200mono_peer_unmap(void* p) {
+  cudaError_t e = cudaIpcCloseMemHandle(p);
+  return e == cudaSuccess ? B200MONO_OK : peer_fail(e, "peer_unmap");
+}
+
+int b200mono_allreduce(const B200AllReduceArgs* a, void* stream) {
+  if (!a || !a->partial || !a->out || !a->peers || !a->words) {
+    set_last_error("allreduce: null pointer");
+    return B200MONO_E_ARG;
+  }
+  if (a->tp < 1 || a->tp > 16 || a->rank < 0 || a->rank >= a->tp || a->rows < 1 || a->rows > a->max_rows ||
+      a->hidden < 4 || a->hidden % 4 || a->slots < 0 || a->slots > 17 || a->phase < 0 || a->phase > 3) {
+    char msg[256];
+    snprintf(msg, sizeof(msg), "allreduce: bad shape tp=%d rank=%d rows=%d max_rows=%d hidden=%d slots=%d phase=%d", a->tp,
+             a->rank, a->rows, a->max_rows, a->hidden, a->slots, a->phase);
+    set_last_error(msg);
+    return B200MONO_E_ARG;
+  }
+  cudaError_t e = launch_allreduce(*a, (cudaStream_t)stream);
+  return e == cudaSuccess ? B200MONO_OK : peer_fail(e, "allreduce");
+}
+
+}  // extern "C"

@@ -1,0 +1,370 @@
+// Expert down projection as a persistent TMA-ring stream, plus the slot-ordered combine.
+//
+// y[u][t, n] = W2[e_u][n, :] . midq[u][t, :] is needed separately for every picked expert,
+// because each contribution is rounded to bf16 after its route weight before the routed
+// sum (which runs in slot order with a bf16 rounding at every add).  The stream kernel
+// therefore writes contrib[slot][t][n] = bf16(y * w) to a small global buffer and a
+// second, tiny kernel walks the slots.  That split is what lets the stream be cut into
+// equal pieces: a stage is 32 KiB of ONE expert's weights (RB = 16 * 8/PP consecutive
+// output rows x the whole K, contiguous in memory because a row is K bytes long), stages
+// are numbered expert-major and every CTA takes one contiguous range of them.  So all SMs
+// stream the same number of bytes to within one stage, and each SM walks linearly through
+// memory (one tensor copy per stage, one page at a time; jumping between experts on every
+// copy instead costs more than half of the bandwidth).
+//
+// Stage anatomy (K = this rank's expert intermediate size, KB = K/128, PP = KB/2):
+//   consumer warp w owns the 16-row tile w / PP of the stage and the k-block pair w % PP.
+//   The ring carries weights only: one tensor copy of [RB rows x K] (two if K > 1024: a
+//   box row is at most 256 words).  The expert's quantised mid rows (L2-resident), the
+//   block scales and the pick bytes come from global memory and are fetched a few stages
+//   ahead into registers, so no global-memory latency sits between the barrier that fills
+//   a stage and the barrier that frees it.
+//   PP > 1: the PP partials of a tile meet in shared memory in pair order.
+#include <cuda.h>
+
+#include "gemv.cuh"
+#include "launch.h"
+#include "tma_ring.cuh"
+
+namespace b200mono {
+
+constexpr int kDownConsumers = 8;  // warps that share one stage
+constexpr int kDownGroups = 2;     // consumer groups; group g drains the stages it = g, g + kDownGroups, ..
+constexpr int kDownThreads = (kDownGroups * kDownConsumers + 1) * 32;
+constexpr int kDownRows = 16;
+
+struct DownP {
+  const uint8_t* midq;  // [cap][T][K]
+  const float* w2s;     // [E+1][H/128][KB]
+  const float* mids;    // [cap][T][KB]
+  const int* union_count;
+  const int* union_ids;
+  const uint8_t* pick;
+  const float* topk_w;
+  __nv_bfloat16* contrib;  // [topk+1][T][H]
+  int rows, hidden, inter, experts, topk;
+  int pp, rb, ncopy;  // warps per 16-row tile, rows per stage, tensor copies per stage
+  uint32_t* status;
+  int stages;
+  unsigned long long* trace;  // timeline marks [4 CTAs][256 stages][8] or null
+};
+
+__global__ __launch_bounds__(kDownThreads, 1) void down_stream_kernel(DownP p, const __grid_constant__ CUtensorMap tm_w) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int K = p.inter, T = p.rows, RB = p.rb, PP = p.pp;
+  const int SB = RB * K;  // weights of a stage (a multiple of 128: K % 256 == 0)
+  uint8_t* ring = smem;
+  float* red = reinterpret_cast<float*>(smem + (size_t)p.stages * SB);  // [groups][2 buffers][8 warps][4][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + kDownGroups * 2 * kDownConsumers * 4 * 32);
+  uint64_t* empty = full + p.stages;
+  __shared__ int abort_flag;
+  __shared__ int s_ids[520];
+  __shared__ float s_w[8 * 17];  // route weights [t][slot], slot topk = shared expert (1.0)
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages;
+  const int U = *p.union_count;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kDownConsumers);
+    }
+    mbar_fence_init();
+  }
+  for (int i = threadIdx.x; i < U; i += kDownThreads) s_ids[i] = p.union_ids[i];
+  for (int i = threadIdx.x; i < T * 17; i += kDownThreads) {
+    const int t = i / 17, sl = i % 17;
+    s_w[i] = sl < p.topk ? p.topk_w[(size_t)t * p.topk + sl] : 1.0f;
+  }
+  __syncthreads();
+  WaitCtx ctx{&abort_flag, p.status};
+
+  const int nblk = p.hidden / RB;  // stages per expert
+  const long long total = (long long)U * nblk;
+  const int su0 = (int)(total * blockIdx.x / gridDim.x), su1 = (int)(total * (blockIdx.x + 1) / gridDim.x);
+  const int CB = K / p.ncopy;  // bytes of a box row
+
+  if (warp == kDownGroups * kDownConsumers) {
+    const uint64_t stream_policy = policy_evict_first();
+    uint32_t it = 0;
+    for (int su = su0; su < su1 && !abort_flag; ++su, ++it) {
+      const int s = it % S;
+      const uint32_t ph = (it / S) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1, ctx, 3))) break;
+      if (lane == 0) {
+        const int u = su / nblk, blk = su % nblk;
+        const int e = s_ids[u];
+        uint8_t* st = ring + (size_t)s * SB;
+        if (p.trace && blockIdx.x < 4 && it < 256) p.trace[((size_t)blockIdx.x * 256 + it) * 8 + 0] = globaltimer_ns();
+        mbar_arrive_expect_tx(&full[s], (uint32_t)SB);
+        for (int ci = 0; ci < p.ncopy; ++ci)
+          tma_2d(st + ci * RB * CB, &tm_w, ci * (CB / 4), e * p.hidden + blk * RB, &full[s], stream_policy);
+        if (p.trace && blockIdx.x < 4 && it < 256) p.trace[((size_t)blockIdx.x * 256 + it) * 8 + 1] = globaltimer_ns();
+      }
+      __syncwarp();
+    }
+    if (abort_flag) {
+      const uint32_t first = it > (uint32_t)S ? it - S : 0;
+      for (uint32_t i = first; i < it; ++i) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (!mbar_try_wait(&full[i % S], (i / S) & 1) && globaltimer_ns() - t0 < 10000000ull) {
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------------------------------------- consumers
+  // Group `grp` drains the stages it = grp, grp + kDownGroups, ..  A CTA's range of stages covers
+  // at most a few experts, and everything that depends only on the expert (this lane's activation
+  // fragment, its block scales, which slot of which row picked the expert, the route weights, the
+  // output addresses) is loaded when the expert changes and then stays in registers; per stage a
+  // warp fetches only its two weight block scales, one stage ahead.
+  const int grp = warp / kDownConsumers, wl = warp % kDownConsumers;
+  const int g = lane >> 2, c4 = lane & 3;
+  const int tl = wl / PP, kp = wl % PP;
+  const bool mine = tl * kDownRows < RB;  // (PP = 3 leaves two warps of a group idle)
+  const int KB = K >> 7;
+  float* gred = red + grp * 2 * kDownConsumers * 4 * 32;
+  bool dead = false;
+  uint32_t frag_off[2];  // this lane's weight fragment inside a stage, per k block of its pair
+#pragma unroll
+  for (int kbi = 0; kbi < 2; ++kbi) {
+    const int kbyte = (kp * 2 + kbi) * 128;
+    const int ci = kbyte / CB;
+    frag_off[kbi] = (uint32_t)(ci * RB * CB + (tl * kDownRows + g) * CB + kbyte - ci * CB + c4 * 32);
+  }
+  auto load_ws = [&](int u, int blk, float (&o)[2]) {
+    const float* wrow = p.w2s + ((size_t)s_ids[u] * (p.hidden >> 7) + ((blk * RB + tl * kDownRows) >> 7)) * KB + kp * 2;
+    o[0] = wrow[0];
+    o[1] = wrow[1];
+  };
+  // per-expert state
+  int cur_u = -1;
+  uint4 x[2][2];
+  float ms[2][2], wgt[2];
+  __nv_bfloat16* cptr[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    x[i][0] = x[i][1] = make_uint4(0, 0, 0, 0);
+    ms[i][0] = ms[i][1] = 0.f;
+    wgt[i] = 0.f;
+    cptr[i] = nullptr;
+  }
+  int su = su0 + grp;
+  int u_c = su / nblk, blk_c = su % nblk;
+  float ws_cur[2] = {0.f, 0.f}, ws_nxt[2] = {0.f, 0.f};
+  if (mine && su < su1) load_ws(u_c, blk_c, ws_cur);
+  uint32_t n = 0;  // stages this group has drained
+  for (; su < su1; su += kDownGroups, ++n) {
+    // position of the group's next stage, without divisions
+    int u_n = u_c, blk_n = blk_c + kDownGroups;
+    while (blk_n >= nblk) {
+      blk_n -= nblk;
+      ++u_n;
+    }
+    if (mine && su + kDownGroups < su1) load_ws(u_n, blk_n, ws_nxt);
+    if (mine && u_c != cur_u) {
+      cur_u = u_c;
+      if (g < T) {
+        const uint8_t* xr = p.midq + ((size_t)u_c * T + g) * K + kp * 256 + c4 * 32;
+        x[0][0] = ld_u4(xr);
+        x[0][1] = ld_u4(xr + 16);
+        x[1][0] = ld_u4(xr + 128);
+        x[1][1] = ld_u4(xr + 144);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int t = 2 * c4 + j;
+        ms[0][j] = ms[1][j] = 0.f;
+        wgt[j] = 0.f;
+        cptr[j] = nullptr;
+        if (t < T) {
+          const float* m = p.mids + ((size_t)u_c * T + t) * KB + kp * 2;
+          ms[0][j] = m[0];
+          ms[1][j] = m[1];
+          const int slot = p.pick[u_c * 32 + t];
+          if (slot) {
+            wgt[j] = s_w[t * 17 + slot - 1];
+            cptr[j] = p.contrib + ((size_t)(slot - 1) * T + t) * p.hidden + tl * kDownRows + g;
+          }
+        }
+      }
+    }
+    const uint32_t it = (uint32_t)(su - su0);
+    const int s = it % S;
+    const uint32_t ph = (it / S) & 1;
+    const bool tr = p.trace && blockIdx.x < 4 && it < 256 && threadIdx.x == 0;
+    unsigned long long* trow = p.trace + ((size_t)blockIdx.x * 256 + (it & 255)) * 8;
+    if (tr) trow[2] = globaltimer_ns();
+    if (!__all_sync(0xffffffffu, mbar_wait(&full[s], ph, ctx, 4))) {
+      dead = true;
+      if (PP == 1) return;  // no named barriers on this path: a warp may leave alone
+    }
+    if (tr) trow[3] = globaltimer_ns();
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!dead && mine) {
+      const uint32_t st = smem_u32(ring + (size_t)s * SB);
+      // per k block: four independent MMAs (a chain through one accumulator would serialise on
+      // the tensor pipe's latency), summed pairwise, then the block scale
+#pragma unroll
+      for (int kbi = 0; kbi < 2; ++kbi) {
+        const uint32_t lo_addr = st + frag_off[kbi];
+        const uint32_t hi_addr = lo_addr + 8 * CB;
+        const uint4 lo0 = lds_u4(lo_addr), lo1 = lds_u4(lo_addr + 16);
+        const uint4 hi0 = lds_u4(hi_addr), hi1 = lds_u4(hi_addr + 16);
+        const uint4 x0 = x[kbi][0], x1 = x[kbi][1];
+        float q0[4] = {0.f, 0.f, 0.f, 0.f}, q1[4] = {0.f, 0.f, 0.f, 0.f}, q2[4] = {0.f, 0.f, 0.f, 0.f},
+              q3[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_e4m3_16x8x32(q0, lo0.x, hi0.x, lo0.y, hi0.y, x0.x, x0.y);
+        mma_e4m3_16x8x32(q1, lo0.z, hi0.z, lo0.w, hi0.w, x0.z, x0.w);
+        mma_e4m3_16x8x32(q2, lo1.x, hi1.x, lo1.y, hi1.y, x1.x, x1.y);
+        mma_e4m3_16x8x32(q3, lo1.z, hi1.z, lo1.w, hi1.w, x1.z, x1.w);
+        const float f0 = ws_cur[kbi] * ms[kbi][0], f1 = ws_cur[kbi] * ms[kbi][1];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = fmaf((q0[i] + q1[i]) + (q2[i] + q3[i]), (i & 1) ? f1 : f0, acc[i]);
+      }
+    }
+    __syncwarp();
+    if (!dead && lane == 0) mbar_arrive(&empty[s]);
+    if (tr) trow[4] = globaltimer_ns();
+
+    if (PP > 1) {
+      // partials of one tile meet in pair order; two buffers, so one barrier per stage is enough
+      float* rb = gred + (n & 1) * kDownConsumers * 4 * 32;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) rb[(wl * 4 + i) * 32 + lane] = acc[i];
+      // every consumer of the group takes the same exit: the barrier also ORs the "a wait gave up" bits
+      if (named_bar_or(2 + grp, kDownConsumers * 32, dead)) return;
+      if (kp == 0 && mine) {  // (an idle leader's partners would lie past the buffer)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float v = acc[i];
+          for (int k2 = 1; k2 < PP; ++k2) v += rb[((wl + k2) * 4 + i) * 32 + lane];
+          acc[i] = v;
+        }
+      }
+    }
+    if (mine && kp == 0) {
+      const int row0 = blk_c * RB;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = i & 1;
+        if (cptr[j]) cptr[j][row0 + ((i & 2) ? 8 : 0)] = __float2bfloat16_rn(__fmul_rn(acc[i], wgt[j]));
+      }
+    }
+    if (tr) trow[5] = globaltimer_ns();
+    u_c = u_n;
+    blk_c = blk_n;
+    ws_cur[0] = ws_nxt[0];
+    ws_cur[1] = ws_nxt[1];
+  }
+}
+
+// out[t, n] = slots summed in order with a bf16 rounding at every add (+ residual), 8 columns per thread
+__global__ __launch_bounds__(256) void moe_combine_kernel(const __nv_bfloat16* contrib, const __nv_bfloat16* residual,
+                                                          __nv_bfloat16* out, int rows, int hidden, int slots) {
+  const int nvec = hidden >> 3;
+  const int v = blockIdx.x * 256 + threadIdx.x;
+  if (v >= rows * nvec) return;
+  const int t = v / nvec, c = v % nvec;
+  float sum[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sum[j] = 0.f;
+  for (int sl = 0; sl < slots; ++sl) {
+    const uint4 q = reinterpret_cast<const uint4*>(contrib + ((size_t)sl * rows + t) * hidden)[c];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sum[2 * j] = round_bf16(__fadd_rn(sum[2 * j], bf16_lo(w[j])));
+      sum[2 * j + 1] = round_bf16(__fadd_rn(sum[2 * j + 1], bf16_hi(w[j])));
+    }
+  }
+  if (residual) {
+    const uint4 q = reinterpret_cast<const uint4*>(residual + (size_t)t * hidden)[c];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sum[2 * j] = round_bf16(__fadd_rn(sum[2 * j], bf16_lo(w[j])));
+      sum[2 * j + 1] = round_bf16(__fadd_rn(sum[2 * j + 1], bf16_hi(w[j])));
+    }
+  }
+  uint4 o;
+  o.x = pack_bf16x2(sum[0], sum[1]);
+  o.y = pack_bf16x2(sum[2], sum[3]);
+  o.z = pack_bf16x2(sum[4], sum[5]);
+  o.w = pack_bf16x2(sum[6], sum[7]);
+  reinterpret_cast<uint4*>(out + (size_t)t * hidden)[c] = o;
+}
+
+bool make_map_u32(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_cols,
+                  uint32_t box_rows);
+
+bool down_stream_ok(const B200MoeDownArgs& a) {
+  const int KB = a.inter / 128;
+  if (a.rows > 8 || a.inter % 256 != 0 || KB / 2 > 8 || a.experts + 1 > 520 || a.topk > 16) return false;
+  const int ncopy = (a.inter + 1023) / 1024;
+  const int rb = 8 / (a.inter / 256) * kDownRows;
+  if (a.inter % (ncopy * 16) != 0 || a.hidden % rb != 0) return false;
+  return true;
+}
+
+cudaError_t launch_moe_down_stream(const B200MoeDownArgs& a, void* contrib, uint32_t* status, int has_shared,
+                                   int union_cap, cudaStream_t s) {
+  (void)union_cap;
+  DownP p{};
+  p.midq = (const uint8_t*)a.midq;
+  p.w2s = a.w2_scale;
+  p.mids = a.mid_scale;
+  p.union_count = a.union_count;
+  p.union_ids = a.union_ids;
+  p.pick = a.union_pick;
+  p.topk_w = a.topk_w;
+  p.contrib = (__nv_bfloat16*)contrib;
+  p.rows = a.rows;
+  p.hidden = a.hidden;
+  p.inter = a.inter;
+  p.experts = a.experts;
+  p.topk = a.topk;
+  p.pp = a.inter / 256;
+  p.rb = 8 / p.pp * kDownRows;
+  p.ncopy = (a.inter + 1023) / 1024;
+  p.status = status;
+  p.trace = (unsigned long long*)timeline_buffer();
+  const int SB = p.rb * a.inter;
+  const size_t fixed = kDownGroups * 2 * kDownConsumers * 4 * 32 * sizeof(float) + 256;
+  const size_t budget = 220 * 1024;
+  int stages = (int)((budget - fixed) / SB);
+  if (stages > 8) stages = 8;
+  if (stages < 2) return cudaErrorInvalidValue;
+  p.stages = stages;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(down_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  CUtensorMap tm_w;
+  const uint32_t box_cols = (uint32_t)(a.inter / p.ncopy / 4);
+  if (!make_map_u32(&tm_w, a.w2, (uint64_t)a.inter / 4, (uint64_t)(a.experts + 1) * a.hidden, (uint64_t)a.inter,
+                    box_cols, (uint32_t)p.rb))
+    return cudaErrorInvalidValue;
+  int sms = 148;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  down_stream_kernel<<<sms, kDownThreads, (size_t)stages * SB + fixed, s>>>(p, tm_w);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int slots = a.topk + (has_shared ? 1 : 0);
+  const int nvec = a.rows * (a.hidden / 8);
+  moe_combine_kernel<<<(nvec + 255) / 256, 256, 0, s>>>((const __nv_bfloat16*)contrib,
+                                                       (const __nv_bfloat16*)a.residual, (__nv_bfloat16*)a.out, a.rows,
+                                                       a.hidden, slots);
+  return cudaGetLastError();
+}
+
+}  // namespace b200mono

@@ -57,7 +57,7 @@ template <int NT>
 constexpr int red_floats() {
   return kConsumers * 2 * NT * 4 * 32;
 }
-// stage: [32 weight rows][NT*8 activation rows] (padded rows), [NT*8][8] activation scales, [2][8] weight scales
+// stage: [32 weight rows][NT*8 activation rows] (1 KiB each), [NT*8][8] activation scales, [2][8] weight scales
 template <int NT>
 constexpr int off_xscale() {
   return (32 + NT * 8) * kRowStride;
@@ -229,16 +229,18 @@ __global__ __launch_bounds__(kThreads, 1) void stream_kernel(StreamP p, const __
           const uint4 hi0 = lds_u4(hi_addr), hi1 = lds_u4(hi_addr + 16);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            float q[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_e4m3_16x8x32(q, lo0.x, hi0.x, lo0.y, hi0.y, x0[nt].x, x0[nt].y);
-            mma_e4m3_16x8x32(q, lo0.z, hi0.z, lo0.w, hi0.w, x0[nt].z, x0[nt].w);
-            mma_e4m3_16x8x32(q, lo1.x, hi1.x, lo1.y, hi1.y, x1[nt].x, x1[nt].y);
-            mma_e4m3_16x8x32(q, lo1.z, hi1.z, lo1.w, hi1.w, x1[nt].z, x1[nt].w);
+            // four independent MMAs (a chain through one accumulator would serialise on the
+            // tensor pipe's latency), summed pairwise, then the block scale
+            float q0[4] = {0.f, 0.f, 0.f, 0.f}, q1[4] = {0.f, 0.f, 0.f, 0.f}, q2[4] = {0.f, 0.f, 0.f, 0.f},
+                  q3[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_e4m3_16x8x32(q0, lo0.x, hi0.x, lo0.y, hi0.y, x0[nt].x, x0[nt].y);
+            mma_e4m3_16x8x32(q1, lo0.z, hi0.z, lo0.w, hi0.w, x0[nt].z, x0[nt].w);
+            mma_e4m3_16x8x32(q2, lo1.x, hi1.x, lo1.y, hi1.y, x1[nt].x, x1[nt].y);
+            mma_e4m3_16x8x32(q3, lo1.z, hi1.z, lo1.w, hi1.w, x1[nt].z, x1[nt].w);
             const float f0 = wsr * s0[nt], f1 = wsr * s1[nt];
-            acc[r][nt][0] = fmaf(q[0], f0, acc[r][nt][0]);
-            acc[r][nt][1] = fmaf(q[1], f1, acc[r][nt][1]);
-            acc[r][nt][2] = fmaf(q[2], f0, acc[r][nt][2]);
-            acc[r][nt][3] = fmaf(q[3], f1, acc[r][nt][3]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              acc[r][nt][i] = fmaf((q0[i] + q1[i]) + (q2[i] + q3[i]), (i & 1) ? f1 : f0, acc[r][nt][i]);
           }
         }
       }
@@ -325,6 +327,11 @@ static bool make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* base, u
   return fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_map_u32(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch, uint32_t box_cols,
+                  uint32_t box_rows) {
+  return make_map(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, base, cols, rows, pitch, box_cols, box_rows);
 }
 
 template <int NT, int MODE>

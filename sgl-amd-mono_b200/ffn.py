@@ -143,7 +143,9 @@ class FfnRunner:
             ("moe_down", cabi.fill("B200MoeDownArgs", midq=at("midq"), mid_scale=at("mids"), w2=self.w.w2,
                                    w2_scale=self.w.w2_s, union_count=at("union_count"), union_ids=at("union_ids"),
                                    union_pick=at("union_pick"), topk_w=at("topk_w"), residual=res, out=out, rows=rows,
-                                   hidden=b.hidden, inter=b.inter, experts=b.experts, topk=b.topk)),
+                                   hidden=b.hidden, inter=b.inter, experts=b.experts, topk=b.topk,
+                                   has_shared=int(b.has_shared), contrib=at("contrib"), status=at("status"),
+                                   union_cap=L.union_cap, variant=0)),
         ]
 
     def status(self) -> int:

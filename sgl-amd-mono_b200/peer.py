@@ -1,0 +1,119 @@
+"""Symmetric peer memory of one tensor-parallel group and the in-kernel all-reduce on it.
+
+Mirrors the reference's ``PeerBuffer`` (sgl_amd_mono/common/peer.py:122-166: allocate, exchange
+IPC handles over a CPU process group, open every peer's handle, keep an int64 address table on
+the device, never free while kernels may still run) on CUDA IPC.  The handshake is collective:
+every rank of ``group`` must construct the buffer at the same point of the program.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import cabi
+
+
+class PeerBuffer:
+    """One inbox per rank, mapped into every rank: ``table[r]`` is rank r's inbox in this process."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, group=None, device=None, lib=None):
+        self.lib = lib or cabi.lib()
+        self.rank, self.world, self.nbytes = rank, world, int(nbytes)
+        self.device = torch.device(device if device is not None else "cuda")
+        self.local = ctypes.c_void_p()
+        self.mapped: dict[int, int] = {}
+        self.closed = False
+        self.lib.call("peer_alloc", self.nbytes, ctypes.byref(self.local))
+        handle = (ctypes.c_ubyte * 64)()
+        if world > 1:
+            self.lib.call("peer_export", self.local, handle)
+        mine = bytes(handle)
+        if world > 1:
+            handles: list = [None] * world
+            dist.all_gather_object(handles, mine, group=group)
+        else:
+            handles = [mine]
+        addrs, err = [], None
+        try:
+            for r, h in enumerate(handles):
+                if r == rank:
+                    addrs.append(self.local.value)
+                    continue
+                p = ctypes.c_void_p()
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                self.lib.call("peer_import", buf, ctypes.byref(p))
+                self.mapped[r] = p.value
+                addrs.append(p.value)
+        except Exception as e:  # noqa: BLE001 - reported after the ranks have agreed
+            err = e
+        # every rank must have mapped every peer before anyone launches a kernel that stores to them;
+        # a rank that failed says so here, so that no rank is left waiting for it
+        if world > 1:
+            ok = torch.tensor([0 if err else 1], dtype=torch.int32)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) != 1:
+                self.close()
+                raise RuntimeError(f"peer handshake failed on rank {rank}: {err}" if err else
+                                   "peer handshake failed on another rank")
+        elif err:
+            raise err
+        self.addrs = addrs
+        self.table = self._table(addrs)
+
+    def _table(self, addrs):
+        return torch.tensor(addrs, dtype=torch.int64, device=self.device)
+
+    def close(self):
+        """Unmap the peers and free the local buffer.  Only after every rank has stopped launching."""
+        if self.closed:
+            return
+        self.closed = True
+        for p in self.mapped.values():
+            self.lib.call("peer_unmap", ctypes.c_void_p(p))
+        self.mapped.clear()
+        self.lib.call("peer_free", self.local)
+
+
+class AllReduce:
+    """Tensor-parallel all-reduce with the residual add fused, run inside one kernel per rank.
+
+    ``run(partial, residual, out)`` enqueues on the current stream; all ranks must enqueue the same
+    sequence of calls.  The epoch that tags the messages lives in device memory and is advanced by
+    the kernel, so a captured CUDA graph replays correctly.
+    """
+
+    def __init__(self, max_rows: int, hidden: int, rank: int, world: int, group=None, device=None, timeout_ms: int = 2000,
+                 lib=None):
+        self.lib = lib or cabi.lib()
+        self.max_rows, self.hidden, self.rank, self.world = max_rows, hidden, rank, world
+        self.timeout_ms = timeout_ms
+        self.device = torch.device(device if device is not None else "cuda")
+        n = ctypes.c_int64()
+        self.lib.call("allreduce_inbox_bytes", world, max_rows, hidden, ctypes.byref(n))
+        self.peer = PeerBuffer(n.value, rank, world, group, self.device, self.lib)
+        self.words = torch.zeros(4, dtype=torch.int32, device=self.device)
+
+    def run(self, partial: torch.Tensor, residual: torch.Tensor | None, out: torch.Tensor, slots: int = 0, phase: int = 0,
+            stream=None):
+        rows = out.shape[0]
+        if not 1 <= rows <= self.max_rows or out.shape[1] != self.hidden:
+            raise ValueError(f"out {tuple(out.shape)} does not fit inboxes sized for [{self.max_rows}, {self.hidden}]")
+        want = (slots, rows, self.hidden) if slots else (rows, self.hidden)
+        if tuple(partial.shape) != want or partial.dtype != torch.bfloat16 or not partial.is_contiguous():
+            raise ValueError(f"partial: expected contiguous bf16 {want}, got {partial.dtype} {tuple(partial.shape)}")
+        a = cabi.fill("B200AllReduceArgs", partial=partial, residual=residual, out=out, peers=self.peer.table,
+                      words=self.words, rows=rows, hidden=self.hidden, tp=self.world, rank=self.rank,
+                      max_rows=self.max_rows, slots=slots, phase=phase, timeout_ms=self.timeout_ms)
+        s = stream or torch.cuda.current_stream(self.device)
+        self.lib.call("allreduce", a, s.cuda_stream)
+        return out
+
+    def status(self) -> int:
+        """0, or (5 << 16 | rank) of the first peer a wait gave up on; synchronises."""
+        return int(self.words[2].item())
+
+    def close(self):
+        self.peer.close()

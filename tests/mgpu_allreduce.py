@@ -1,0 +1,89 @@
+"""Multi-process check of the in-kernel all-reduce (launched by torch.distributed.run, one rank per GPU):
+every rank's output equals the rank-ordered f32 sum + residual, all ranks agree bit for bit, a captured
+CUDA graph replays with fresh epochs, and the sweep hidden 7168 x rows {1..32} is timed on the device."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import sgl_amd_mono_b200  # noqa: E402,F401
+from oracle import collective as C  # noqa: E402
+from sgl_amd_mono_b200.peer import AllReduce  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    cpu = dist.new_group(backend="gloo")
+    hidden = 7168
+    ar = AllReduce(32, hidden, rank, world, group=cpu, device=dev)
+    g = torch.Generator().manual_seed(3)
+    for rows in (1, 8, 32):
+        for step in range(3):
+            parts = [(torch.randn(rows, hidden, generator=g) * (1 + r)).bfloat16() for r in range(world)]
+            res = torch.randn(rows, hidden, generator=g).bfloat16()
+            out = torch.full((rows, hidden), float("nan"), dtype=torch.bfloat16, device=dev)
+            ar.run(parts[rank].to(dev), res.to(dev), out)
+            torch.cuda.synchronize()
+            assert ar.status() == 0
+            assert torch.equal(out.cpu(), C.allreduce(parts, res)), (rank, rows, step)
+    # graph replay: the epoch lives on the device
+    rows = 8
+    part = torch.randn(rows, hidden, generator=g).bfloat16().to(dev) * (rank + 1)
+    res = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=dev)
+    out = torch.empty_like(res)
+    s = torch.cuda.Stream(dev)
+    with torch.cuda.stream(s):
+        ar.run(part, res, out)
+        s.synchronize()
+        first = out.clone()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=s):
+            ar.run(part, res, out)
+        for _ in range(50):
+            gr.replay()
+        s.synchronize()
+    assert ar.status() == 0 and torch.equal(out, first)
+    # sweep, device-timed, max over ranks
+    lines = []
+    for rows in (1, 2, 4, 8, 16, 32):
+        part = torch.randn(rows, hidden, generator=g).bfloat16().to(dev)
+        res = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=dev)
+        out = torch.empty_like(res)
+        with torch.cuda.stream(s):
+            gr = torch.cuda.CUDAGraph()
+            ar.run(part, res, out)
+            s.synchronize()
+            with torch.cuda.graph(gr, stream=s):
+                for _ in range(20):
+                    ar.run(part, res, out)
+            gr.replay()
+            s.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            for _ in range(10):
+                gr.replay()
+            e1.record(s)
+            s.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1000 / 200], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out_bytes = rows * hidden * 4 * (world - 1)  # tagged words are twice the payload
+        lines.append(f"rows={rows:2d} {t.item():7.2f} us  {out_bytes / t.item() / 1e3:7.1f} GB/s out per rank")
+    if rank == 0:
+        print(f"allreduce sweep tp={world} hidden={hidden}:")
+        print("\n".join(lines))
+        print("allreduce ok")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

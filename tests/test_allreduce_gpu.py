@@ -1,0 +1,103 @@
+"""The in-kernel all-reduce: rank-ordered f32 sum + residual, identical bits on every rank.
+
+On one GPU the ranks are emulated with the kernel's two phases (all pushes, then all reduces, as
+consecutive launches over tp inboxes that live on the same device): kernels that wait on one
+another must never run as separate launches on one GPU.  With two or more GPUs a real
+two-process run over CUDA IPC peer memory is added (skipped otherwise)."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import sgl_amd_mono_b200  # noqa: F401
+from oracle import collective as C
+from sgl_amd_mono_b200 import cabi
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class Emulated:
+    """tp ranks on one device: one inbox and one word block per rank, one shared address table."""
+
+    def __init__(self, lib, tp, max_rows, hidden):
+        import ctypes
+
+        n = ctypes.c_int64()
+        lib.call("allreduce_inbox_bytes", tp, max_rows, hidden, ctypes.byref(n))
+        self.lib, self.tp, self.max_rows, self.hidden = lib, tp, max_rows, hidden
+        self.inbox = [torch.zeros(n.value, dtype=torch.uint8, device=DEV) for _ in range(tp)]
+        self.table = torch.tensor([b.data_ptr() for b in self.inbox], dtype=torch.int64, device=DEV)
+        self.words = [torch.zeros(4, dtype=torch.int32, device=DEV) for _ in range(tp)]
+
+    def call(self, r, partial, residual, out, phase, slots=0, timeout_ms=2000):
+        a = cabi.fill("B200AllReduceArgs", partial=partial, residual=residual, out=out, peers=self.table,
+                      words=self.words[r], rows=out.shape[0], hidden=self.hidden, tp=self.tp, rank=r,
+                      max_rows=self.max_rows, slots=slots, phase=phase, timeout_ms=timeout_ms)
+        self.lib.call("allreduce", a, torch.cuda.current_stream().cuda_stream)
+
+    def step(self, partials, residual, slots=0):
+        outs = [torch.full_like(residual, float("nan")) for _ in range(self.tp)]
+        for r in range(self.tp):
+            self.call(r, partials[r], residual, outs[r], 1, slots)
+        for r in range(self.tp):
+            self.call(r, partials[r], residual, outs[r], 2, slots)
+        torch.cuda.synchronize()
+        return outs
+
+
+@pytest.mark.parametrize("tp,rows,hidden", [(1, 4, 2048), (2, 8, 7168), (4, 1, 7168), (8, 8, 7168), (8, 32, 7168), (3, 5, 512)])
+def test_emulated_ranks_agree_with_the_rank_ordered_sum(lib, tp, rows, hidden):
+    em = Emulated(lib, tp, 32, hidden)
+    g = torch.Generator().manual_seed(tp * 100 + rows)
+    for step in range(3):  # epochs 0, 1, 2: both parity halves and their reuse
+        parts = [(torch.randn(rows, hidden, generator=g) * (1 + r)).bfloat16().to(DEV) for r in range(tp)]
+        res = torch.randn(rows, hidden, generator=g).bfloat16().to(DEV)
+        outs = em.step(parts, res)
+        want = C.allreduce(parts, res)
+        for r in range(tp):
+            assert torch.equal(outs[r].cpu(), want), f"rank {r} step {step}"
+            assert em.words[r].tolist()[:3] == [step + 1, 0, 0]
+
+
+def test_slot_ordered_combine_fused_into_the_push(lib):
+    tp, rows, hidden, slots = 2, 8, 7168, 9
+    em = Emulated(lib, tp, 8, hidden)
+    g = torch.Generator().manual_seed(5)
+    contribs = [torch.randn(slots, rows, hidden, generator=g).bfloat16().to(DEV) for _ in range(tp)]
+    res = torch.randn(rows, hidden, generator=g).bfloat16().to(DEV)
+    outs = em.step(contribs, res, slots=slots)
+    want = C.allreduce([C.slot_sum(c) for c in contribs], res)
+    assert torch.equal(outs[0].cpu(), want) and torch.equal(outs[1].cpu(), want)
+
+
+def test_a_peer_that_never_publishes_ends_with_a_status_not_a_hang(lib):
+    tp, rows, hidden = 2, 4, 2048
+    em = Emulated(lib, tp, 8, hidden)
+    part = torch.ones(rows, hidden, dtype=torch.bfloat16, device=DEV)
+    out = torch.full_like(part, float("nan"))
+    em.call(0, part, None, out, 1)            # rank 0 pushes, rank 1 never does
+    em.call(0, part, None, out, 2, timeout_ms=50)
+    torch.cuda.synchronize()
+    status = int(em.words[0][2].item())
+    assert status == (5 << 16) | 1            # gave up waiting for rank 1
+    assert not torch.isnan(out.float()).any()  # zeros were written for what could not be summed
+    # the context is still usable and the epoch advanced: the next exchange is clean
+    em.words[0][2] = 0
+    em.words[1][0] = em.words[0][0]
+    outs = em.step([part, part], torch.zeros_like(part))
+    assert torch.equal(outs[0], outs[1]) and float(outs[0][0, 0]) == 2.0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_processes_over_cuda_ipc():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29631", os.path.join(ROOT, "tests", "mgpu_allreduce.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "allreduce ok" in r.stdout

@@ -1,0 +1,97 @@
+"""Host logic of the symmetric peer buffer with a fake C ABI: world_size-2 gloo ranks on CPU.
+
+The fake stands in for the CUDA IPC calls (as the reference tests PeerBuffer.close with a fake
+HIP runtime, test/unit/test_common_peer.py:13-44); it records every call so the tests can check
+the handshake order, the address table, the unmap/free bookkeeping and the failure path in which
+one rank cannot map a peer and every rank must leave the handshake with an error, not hang."""
+
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class FakeLib:
+    def __init__(self, rank, fail_import_on=None):
+        self.rank, self.fail_import_on, self.calls = rank, fail_import_on, []
+
+    def call(self, name, *args):
+        self.calls.append(name)
+        if name == "peer_alloc":
+            args[1]._obj.value = 0x1000 * (self.rank + 1)
+        elif name == "peer_export":
+            args[1][0] = self.rank + 1
+        elif name == "peer_import":
+            if self.fail_import_on == self.rank:
+                raise RuntimeError("peer access unavailable")
+            args[1]._obj.value = 0x100000 + 0x1000 * args[0][0]
+        elif name == "allreduce_inbox_bytes":
+            args[3]._obj.value = 2 * args[0] * args[1] * (args[2] // 4) * 16
+        return 0
+
+
+def _worker(rank, world, port, fail_on, q):
+    sys.path.insert(0, ROOT)
+    import sgl_amd_mono_b200  # noqa: F401
+    from sgl_amd_mono_b200.peer import PeerBuffer
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    lib = FakeLib(rank, fail_on)
+    try:
+        pb = PeerBuffer(4096, rank, world, device="cpu", lib=lib)
+        table = pb.table.tolist()
+        pb.close()
+        pb.close()
+        q.put((rank, "ok", table, lib.calls))
+    except RuntimeError as e:
+        q.put((rank, "error", str(e), lib.calls))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _run(fail_on, port):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, fail_on, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return out
+
+
+def test_handshake_builds_the_address_table_and_closes_once():
+    (r0, s0, t0, c0), (r1, s1, t1, c1) = _run(None, 29611)
+    assert s0 == s1 == "ok"
+    # own inbox at the local address, the peer's at the mapped one
+    assert t0 == [0x1000, 0x100000 + 0x1000 * 2] and t1 == [0x100000 + 0x1000 * 1, 0x2000]
+    for calls in (c0, c1):
+        assert calls == ["peer_alloc", "peer_export", "peer_import", "peer_unmap", "peer_free"]
+
+
+def test_a_rank_that_cannot_map_its_peer_stops_every_rank():
+    (r0, s0, m0, c0), (r1, s1, m1, c1) = _run(1, 29612)
+    assert s0 == s1 == "error"
+    assert "another rank" in m0 and "peer access unavailable" in m1
+    # both ranks released what they held
+    assert c0[-2:] == ["peer_unmap", "peer_free"] and c1[-1] == "peer_free"
+
+
+def test_single_rank_needs_no_handshake():
+    sys.path.insert(0, ROOT)
+    import sgl_amd_mono_b200  # noqa: F401
+    from sgl_amd_mono_b200.peer import PeerBuffer
+
+    lib = FakeLib(0)
+    pb = PeerBuffer(1024, 0, 1, device="cpu", lib=lib)
+    assert pb.table.tolist() == [0x1000] and lib.calls == ["peer_alloc"]
+    pb.close()
+    assert lib.calls == ["peer_alloc", "peer_free"]
