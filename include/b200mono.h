@@ -81,6 +81,8 @@ typedef struct {
   int32_t rows, hidden; /* hidden % 128 == 0, hidden <= 16384 */
   float eps;
   int32_t gemma;        /* 1: multiply by (1 + w) instead of w */
+  int32_t x_stride;     /* elements between input rows of x (0 = hidden); a multiple of 8 */
+  int32_t pad_;
 } B200NormQuantArgs;
 int b200mono_norm_quant(const B200NormQuantArgs* a, void* stream);
 
@@ -200,6 +202,9 @@ typedef struct {
   uint32_t* status;         /* u32 [1] or NULL: as in B200GemvFp8Args */
   int32_t union_cap;        /* entries of midq / mid_scale (their first dimension) */
   int32_t variant;          /* 0: pick automatically; 1: one CTA per 16 rows; 2: persistent TMA-ring kernel */
+  int32_t skip_combine;     /* 1 (persistent kernel only): stop after writing contrib; the caller sums the slots,
+                               e.g. the all-reduce with slots > 0 */
+  int32_t pad_;
 } B200MoeDownArgs;
 int b200mono_moe_down(const B200MoeDownArgs* a, void* stream);
 
@@ -277,6 +282,111 @@ int b200mono_peer_free(void* p);
 int b200mono_peer_export(void* p, void* handle64);
 int b200mono_peer_import(const void* handle64, void** out);
 int b200mono_peer_unmap(void* p);
+
+/* ------------------------------------------------------------------------
+ * Sparse-MLA attention side.  Formats: a KV record is 656 bytes (512 e4m3 latent, 4 f32
+ * scales one per 128 dims, 64 bf16 RoPE'd key dims); an index page is 4352 bytes for 64
+ * token slots ([64][64] bytes of packed E2M1 codes, low nibble = even dim, then [64][4]
+ * E8M0 codes, one per 32 dims).  Slot s is record s of the KV cache and entry s % 64 of
+ * index page s / 64; slots <= 0 are pad rows and write nothing (cf. the paged FP8 latent
+ * cache and pad slot of sgl_amd_mono/glm53/gfx950/runner.py:28-32,118-121 and
+ * test/kernels/glm53/check_layer.py:248-261).  RoPE is the GPT-J interleaved rotation
+ * with an f32 table [position][32 cos | 32 sin]
+ * (sgl_amd_mono/deepseek_v41/gfx950/weights.py:34-43).
+ */
+/* KV record + index-key record write: replaces front.stage_qkv / record_scales
+ * (sgl_amd_mono/deepseek_v41/gfx950/attention/front.py:196-368) and glm53 section 3
+ * (sgl_amd_mono/glm53/gfx950/kernel.py:3174-3283). */
+typedef struct {
+  const void* kv_q;          /* e4m3 [rows, 512]: normed latent, per-128 quantised */
+  const float* kv_scale;     /* f32 [rows, 4] */
+  const void* ya;            /* bf16 [rows, ldya]: output of the fused q_a/kv_a projection */
+  const int32_t* positions;  /* int32 [rows] */
+  const int32_t* slots;      /* int32 [rows]: cache slot of the row's token (<= 0: pad) */
+  const float* rope_table;   /* f32 [max_pos, 64] */
+  void* kv_cache;            /* u8 [slots, 656] */
+  void* idx_cache;           /* u8 [pages, 4352] */
+  int32_t rows, ldya;
+  int32_t col_rope;          /* first of the 64 key position columns in ya */
+  int32_t col_idx;           /* first of the 128 index-key columns in ya */
+} B200KvWriteArgs;
+int b200mono_kv_write(const B200KvWriteArgs* a, void* stream);
+
+/* Per head: FP8 quant (per 128) of the 128 no-position dims and RoPE of the 64 position dims:
+ * replaces front.stage_wqb's epilogue (sgl_amd_mono/deepseek_v41/gfx950/attention/front.py:443-476;
+ * torch: test/kernels/deepseek_v41/check_k1.py:97-125). */
+typedef struct {
+  const void* q;             /* bf16 [rows, heads*192] */
+  const int32_t* positions;
+  const float* rope_table;
+  void* qn_q;                /* e4m3 [rows, heads*128] */
+  float* qn_scale;           /* f32 [rows, heads] */
+  void* q_rope;              /* bf16 [rows, heads*64] */
+  int32_t rows, heads;
+} B200QPostArgs;
+int b200mono_q_post(const B200QPostArgs* a, void* stream);
+
+/* Index query: RoPE on dims 64..127, MXFP4 per 32 dims, head weights: replaces
+ * sgl_amd_mono/deepseek_v41/gfx950/attention/index_query.py:180-345. */
+typedef struct {
+  const void* qi;            /* bf16 [rows, heads*128] */
+  const void* ya;            /* bf16 [rows, ldya] (holds the head-weight columns) */
+  const int32_t* positions;
+  const float* rope_table;
+  void* q_rec;               /* u8 [rows, heads, 68]: 64 code bytes + 4 E8M0 codes */
+  float* w;                  /* f32 [rows, heads] */
+  int32_t rows, heads, ldya, col_w;
+  float weight_scale;
+  int32_t pad_;
+} B200IdxQPostArgs;
+int b200mono_idx_q_post(const B200IdxQPostArgs* a, void* stream);
+
+/* Index scores score[t, c] = sum_h w[t,h] relu(q[t,h] . k[c]) over the row's context:
+ * replaces score_fp4 (sgl_amd_mono/deepseek_v41/gfx950/indexer/score_fp4.py:254-410);
+ * torch: test/kernels/test_deepseek_v41_k2i.py:149-167.  64 heads. */
+typedef struct {
+  const void* q_rec;         /* u8 [rows, 64, 68] */
+  const float* w;            /* f32 [rows, 64] */
+  const void* idx_cache;     /* u8 [pages, 4352] */
+  const int32_t* page_table; /* int32 [requests, max_pages] */
+  const int32_t* req_of_row; /* int32 [rows] */
+  const int32_t* ctx_len;    /* int32 [rows]: keys visible to the row (its position + 1) */
+  float* scores;             /* f32 [rows, score_stride] out */
+  int32_t rows, max_pages, max_ctx, score_stride;
+} B200IndexScoreArgs;
+int b200mono_index_score(const B200IndexScoreArgs* a, void* stream);
+
+/* Exact top-k of each row's scores by (score descending, position ascending), positions in
+ * ascending order; rows with at most k keys take all: replaces the radix select of
+ * sgl_amd_mono/glm53/gfx950/kernel.py:4315-4885; torch: sgl_amd_mono/glm53/check.py:111-134. */
+typedef struct {
+  const float* scores;       /* f32 [rows, score_stride] */
+  const int32_t* ctx_len;
+  int32_t* topk_idx;         /* int32 [rows, k] out: positions */
+  int32_t* topk_count;       /* int32 [rows] out: min(k, ctx_len) */
+  int32_t rows, k, score_stride, pad_;
+} B200TopkArgs;
+int b200mono_topk(const B200TopkArgs* a, void* stream);
+
+/* Sparse MLA over the selected entries, `heads` local heads (a multiple of 16): replaces back.stage_split/stage_combine
+ * (sgl_amd_mono/deepseek_v41/gfx950/attention/back.py:181-510) and glm53 sections 5-6
+ * (sgl_amd_mono/glm53/gfx950/kernel.py:4885-5390); torch: test/kernels/deepseek_v41/check_k2.py:118-137. */
+typedef struct {
+  const void* q_lat;         /* bf16 [rows, heads, 512]: absorbed queries */
+  const void* q_rope;        /* bf16 [rows, heads, 64] */
+  const void* kv_cache;      /* u8 [slots, 656] */
+  const int32_t* page_table;
+  const int32_t* req_of_row;
+  const int32_t* topk_idx;   /* int32 [rows, k] positions, ascending */
+  const int32_t* topk_count;
+  void* part_o;              /* bf16 [rows, max_chunks, heads, 512] scratch */
+  float* part_ml;            /* f32 [rows, max_chunks, heads, 2] scratch */
+  void* o_lat;               /* bf16 [rows, heads, 512] out */
+  int32_t rows, k, max_pages, max_chunks; /* max_chunks = ceil(k / 64) */
+  float scale;
+  int32_t heads;
+} B200SparseMlaArgs;
+int b200mono_sparse_mla(const B200SparseMlaArgs* a, void* stream);
 
 /* ------------------------------------------------------------------------
  * The same block for callers that cannot allocate device memory.  This entry

@@ -1,0 +1,149 @@
+"""Sparse-MLA attention side of the decoder layer: RoPE, KV / index-key records, index scores,
+exact top-k, sparse MLA over the selected FP8 latent entries.
+
+Formats (this library's own, fixed here because the benchmark weights and caches are synthetic;
+the arithmetic rules follow the reference's torch goldens cited per function):
+  KV record, 656 bytes: 512 e4m3 latent | 4 f32 scales (one per 128 dims) | 64 bf16 RoPE'd key dims.
+  Index-key record, 68 bytes: 64 bytes of packed E2M1 (low nibble = even dim) | 4 E8M0 codes (one per 32 dims).
+  A page holds 64 consecutive token slots; slot s lives in page s // 64 at s % 64; page 0 is the pad page.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import detmath as dm
+from . import quant as Q
+
+KV_LORA, ROPE, NOPE, V_HEAD = 512, 64, 128, 128
+KV_REC = KV_LORA + 16 + 2 * ROPE  # 656
+IDX_DIM, IDX_REC = 128, 68
+PAGE = 64
+
+
+def rope_table(max_pos: int, dim: int = ROPE, base: float = 10000.0) -> torch.Tensor:
+    """f32 [pos, dim]: dim/2 cosines then dim/2 sines (sgl_amd_mono/deepseek_v41/gfx950/weights.py:34-43)."""
+    inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
+    return torch.cat([ang.cos(), ang.sin()], 1).float()
+
+
+def rope_gptj(x: torch.Tensor, pos: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """GPT-J (interleaved pair) rotation of the last dim (64) of bf16 `x` [rows, ..., 64]; every product and
+    the final add/sub is one f32 rounding, the result is rounded to bf16
+    (test/kernels/deepseek_v41/check_k1.py:121-125; sgl_amd_mono/deepseek_v41/gfx950/attention/index_query.py:235-250)."""
+    xf = x.float().numpy().astype(np.float32)
+    half = table.shape[1] // 2
+    cs = table[pos.long()].numpy().astype(np.float32)  # [rows, 64]
+    shape = [xf.shape[0]] + [1] * (xf.ndim - 2) + [half]
+    c, s = cs[:, :half].reshape(shape), cs[:, half:].reshape(shape)
+    v0, v1 = xf[..., 0::2], xf[..., 1::2]
+    o0 = ((v0 * c).astype(np.float32) - (v1 * s).astype(np.float32)).astype(np.float32)
+    o1 = ((v0 * s).astype(np.float32) + (v1 * c).astype(np.float32)).astype(np.float32)
+    out = np.empty_like(xf)
+    out[..., 0::2], out[..., 1::2] = o0, o1
+    return torch.from_numpy(out).to(torch.bfloat16)
+
+
+# ----------------------------------------------------------------------------- records
+def kv_record(kv_q: torch.Tensor, kv_s: torch.Tensor, k_rope: torch.Tensor) -> torch.Tensor:
+    """u8 [rows, 656] from e4m3 [rows, 512], f32 [rows, 4], bf16 [rows, 64]
+    (format after sgl_amd_mono/deepseek_v41/gfx950/attention/plan.py:27-28 and the 656-byte entry of
+    the FP8 latent cache; quant rule = per-128 amax/448 of the normed latent)."""
+    rows = kv_q.shape[0]
+    rec = torch.empty(rows, KV_REC, dtype=torch.uint8)
+    rec[:, :KV_LORA] = kv_q.view(torch.uint8)
+    rec[:, KV_LORA:KV_LORA + 16] = kv_s.contiguous().view(torch.uint8).reshape(rows, 16)
+    rec[:, KV_LORA + 16:] = k_rope.contiguous().view(torch.uint8).reshape(rows, 2 * ROPE)
+    return rec
+
+
+def kv_dequant(rec: torch.Tensor):
+    """records u8 [n, 656] -> (latent f32 [n, 512] = e4m3 * scale, then rounded to bf16; rope bf16->f32 [n, 64])
+    (dequant to bf16 before the MMA: sgl_amd_mono/deepseek_v41/gfx950/attention/back.py:224-253)."""
+    n = rec.shape[0]
+    q = rec[:, :KV_LORA].contiguous().view(torch.float8_e4m3fn).float().reshape(n, 4, 128)
+    s = rec[:, KV_LORA:KV_LORA + 16].contiguous().view(torch.float32).reshape(n, 4, 1)
+    lat = (q * s).reshape(n, KV_LORA).to(torch.bfloat16).float()
+    rope = rec[:, KV_LORA + 16:].contiguous().view(torch.bfloat16).float().reshape(n, ROPE)
+    return lat, rope
+
+
+def index_record(k: torch.Tensor) -> torch.Tensor:
+    """bf16 [rows, 128] (already rotated) -> u8 [rows, 68]: MXFP4 per 32 dims
+    (scale and code rules: sgl_amd_mono/muse_spark/mxfp4_quant.py:36-61)."""
+    p, s = Q.quantize_mxfp4(k.float())
+    return torch.cat([p, s], 1)
+
+
+def index_dequant(rec: torch.Tensor) -> torch.Tensor:
+    return Q.dequantize_mxfp4(rec[..., :64], rec[..., 64:68])
+
+
+# ----------------------------------------------------------------------------- index scores + top-k
+def index_scores(q_rec: torch.Tensor, w: torch.Tensor, k_rec: torch.Tensor) -> np.ndarray:
+    """logit[c] = sum_h w[h] * relu(sum_g 2^(qe[h,g]+ke[c,g]) * sum_{d in g} q[h,d] k[c,d])  (f32)
+    for one row: q_rec u8 [heads, 68], w f32 [heads], k_rec u8 [ctx, 68]
+    (test/kernels/test_deepseek_v41_k2i.py:149-167 `ref_logits`).
+    Order: the 32-dim group sums are exact (multiples of 1/4 below 2^11); groups are added g = 0..3 after
+    scaling; heads are added in the kernel's order: for each 16-head tile, lanes hold heads (i, i+8), the pair
+    is added first, then an xor tree over i (4, 2, 1), then tiles 0..3 in order."""
+    qv = Q.dequantize_mxfp4(q_rec[:, :64], torch.full_like(q_rec[:, 64:68], 127)).numpy().astype(np.float32)
+    kv = Q.dequantize_mxfp4(k_rec[:, :64], torch.full_like(k_rec[:, 64:68], 127)).numpy().astype(np.float32)
+    qs = np.exp2(q_rec[:, 64:68].numpy().astype(np.float32) - 127).astype(np.float32)  # [H, 4]
+    ks = np.exp2(k_rec[:, 64:68].numpy().astype(np.float32) - 127).astype(np.float32)  # [C, 4]
+    H, C = qv.shape[0], kv.shape[0]
+    acc = np.zeros((H, C), np.float32)
+    for g in range(4):
+        part = (qv[:, 32 * g:32 * g + 32] @ kv[:, 32 * g:32 * g + 32].T).astype(np.float32)  # exact
+        sc = (qs[:, g:g + 1] * ks[None, :, g]).astype(np.float32)
+        acc = (acc + (part * sc).astype(np.float32)).astype(np.float32)
+    term = (np.maximum(acc, 0) * w.numpy().astype(np.float32)[:, None]).astype(np.float32)  # [H, C]
+    tot = np.zeros(C, np.float32)
+    for tile in range(H // 16):
+        t = term[16 * tile:16 * tile + 16]
+        pair = (t[:8] + t[8:]).astype(np.float32)  # heads (i, i+8)
+        for off in (4, 2, 1):
+            idx = np.arange(8) ^ off
+            pair = (pair + pair[idx]).astype(np.float32)
+        tot = (tot + pair[0]).astype(np.float32)
+    return tot
+
+
+def exact_topk(scores: np.ndarray, k: int) -> np.ndarray:
+    """Positions of the exact top-k by (score descending, position ascending) on the radix key of the f32
+    bits, returned in ascending position order; all positions when there are at most k
+    (sgl_amd_mono/glm53/check.py:117-134; test/kernels/glm53/check_topk.py:116-147)."""
+    n = scores.shape[0]
+    if n <= k:
+        return np.arange(n, dtype=np.int32)
+    key = dm.radix_key(scores).astype(np.int64)
+    order = np.lexsort((np.arange(n), -key))[:k]
+    return np.sort(order).astype(np.int32)
+
+
+# ----------------------------------------------------------------------------- sparse MLA
+def sparse_mla(q_lat: torch.Tensor, q_rope: torch.Tensor, recs: torch.Tensor, scale: float, chunk: int = 64):
+    """One row: q_lat bf16 [heads, 512], q_rope bf16 [heads, 64], recs u8 [n, 656] (the selected entries in
+    ascending position order) -> o_lat bf16 [heads, 512].
+    Flash-decoding restated: per chunk of `chunk` entries a split-local softmax (own max m, sum l of the
+    unrounded probabilities, P rounded to bf16 for the PV product, f32 accumulation), partials merged with
+    w = exp(m_c - M) / sum_c l_c exp(m_c - M)
+    (sgl_amd_mono/glm53/gfx950/kernel.py:5172-5389; test/kernels/deepseek_v41/check_k2.py:118-137)."""
+    lat, rope = kv_dequant(recs)
+    ql, qr = q_lat.float(), q_rope.float()
+    s = (ql @ lat.T + qr @ rope.T) * scale  # [heads, n]
+    n = s.shape[1]
+    parts = []
+    for c0 in range(0, n, chunk):
+        sc = s[:, c0:c0 + chunk]
+        m = sc.amax(1, keepdim=True)
+        p = torch.exp(sc - m)
+        l = p.sum(1, keepdim=True)
+        o = (p.to(torch.bfloat16).float() @ lat[c0:c0 + chunk]).to(torch.bfloat16).float()  # partial stored bf16
+        parts.append((m, l, o))
+    M = torch.stack([m for m, _, _ in parts]).amax(0)
+    den = sum(l * torch.exp(m - M) for m, l, _ in parts)
+    out = sum(o * torch.exp(m - M) for m, _, o in parts) / den
+    return out.to(torch.bfloat16)

@@ -59,7 +59,10 @@ int b200mono_abi_sizes(int32_t* out, int32_t capacity) {
                            (int32_t)sizeof(B200GemvFp8Args),   (int32_t)sizeof(B200RouterArgs),
                            (int32_t)sizeof(B200MoeUpArgs),     (int32_t)sizeof(B200MoeDownArgs),
                            (int32_t)sizeof(B200MoeFfnLayout),  (int32_t)sizeof(B200MoeFfnArgs),
-                           (int32_t)sizeof(B200AllReduceArgs)};
+                           (int32_t)sizeof(B200AllReduceArgs),
+                           (int32_t)sizeof(B200KvWriteArgs),   (int32_t)sizeof(B200QPostArgs),
+                           (int32_t)sizeof(B200IdxQPostArgs),  (int32_t)sizeof(B200IndexScoreArgs),
+                           (int32_t)sizeof(B200TopkArgs),      (int32_t)sizeof(B200SparseMlaArgs)};
   const int32_t n = (int32_t)(sizeof(sizes) / sizeof(sizes[0]));
   for (int32_t i = 0; i < n && i < capacity; ++i) out[i] = sizes[i];
   return n;
@@ -82,6 +85,8 @@ int b200mono_norm_quant(const B200NormQuantArgs* a, void* stream) {
   REQUIRE(a->x && a->weight && a->q && a->q_scale, "norm_quant: null pointer");
   REQUIRE(a->rows >= 0 && a->hidden > 0 && a->hidden % 128 == 0 && a->hidden <= 16384,
           "norm_quant: hidden=%d must be a multiple of 128 and <= 16384", a->hidden);
+  REQUIRE(a->x_stride == 0 || (a->x_stride >= a->hidden && a->x_stride % 8 == 0 && !a->residual),
+          "norm_quant: x_stride=%d must be 0 or a multiple of 8 >= hidden (and no residual)", a->x_stride);
   REQUIRE(aligned(a->x, 16) && aligned(a->weight, 16) && aligned(a->q, 8) &&
               (!a->residual || aligned(a->residual, 16)) && (!a->y || aligned(a->y, 16)) &&
               (!a->res_out || aligned(a->res_out, 16)),
@@ -171,11 +176,67 @@ int b200mono_moe_down(const B200MoeDownArgs* a, void* stream) {
   REQUIRE(a->variant >= 0 && a->variant <= 2, "moe_down: variant=%d outside 0..2", a->variant);
   const bool ring_ok = a->contrib && a->union_cap >= 1 && down_stream_ok(*a) && aligned(a->contrib, 16) &&
                        aligned(a->out, 16) && (!a->residual || aligned(a->residual, 16));
+  REQUIRE(!a->skip_combine || (ring_ok && a->variant != 1), "moe_down: skip_combine needs the persistent kernel");
   REQUIRE(a->variant != 2 || ring_ok, "moe_down: variant=2 not available for this shape (rows <= 8, inter %% 256 == 0, contrib given)");
   if (a->variant != 1 && ring_ok)
     return cuda_status(launch_moe_down_stream(*a, a->contrib, a->status, a->has_shared, a->union_cap, (cudaStream_t)stream),
                        "moe_down(ring)");
   return cuda_status(launch_moe_down(*a, (cudaStream_t)stream), "moe_down");
+}
+
+int b200mono_kv_write(const B200KvWriteArgs* a, void* stream) {
+  REQUIRE(a && a->kv_q && a->kv_scale && a->ya && a->positions && a->slots && a->rope_table && a->kv_cache && a->idx_cache,
+          "kv_write: null pointer");
+  REQUIRE(a->rows >= 1 && a->ldya >= 192 && a->col_rope >= 0 && a->col_rope % 2 == 0 && a->col_rope + 64 <= a->ldya &&
+              a->col_idx >= 0 && a->col_idx + 128 <= a->ldya,
+          "kv_write: bad column layout (ldya=%d col_rope=%d col_idx=%d)", a->ldya, a->col_rope, a->col_idx);
+  REQUIRE(aligned(a->kv_q, 16) && aligned(a->kv_scale, 16) && aligned(a->kv_cache, 16) && aligned(a->idx_cache, 16),
+          "kv_write: kv_q, kv_scale and the caches must be 16-byte aligned");
+  return cuda_status(launch_kv_write(*a, (cudaStream_t)stream), "kv_write");
+}
+
+int b200mono_q_post(const B200QPostArgs* a, void* stream) {
+  REQUIRE(a && a->q && a->positions && a->rope_table && a->qn_q && a->qn_scale && a->q_rope, "q_post: null pointer");
+  REQUIRE(a->rows >= 1 && a->heads >= 1, "q_post: rows=%d heads=%d", a->rows, a->heads);
+  REQUIRE(aligned(a->q, 16) && aligned(a->qn_q, 4) && aligned(a->q_rope, 4), "q_post: q must be 16-byte aligned");
+  return cuda_status(launch_q_post(*a, (cudaStream_t)stream), "q_post");
+}
+
+int b200mono_idx_q_post(const B200IdxQPostArgs* a, void* stream) {
+  REQUIRE(a && a->qi && a->ya && a->positions && a->rope_table && a->q_rec && a->w, "idx_q_post: null pointer");
+  REQUIRE(a->rows >= 1 && a->heads >= 1 && a->col_w >= 0 && a->col_w + a->heads <= a->ldya,
+          "idx_q_post: rows=%d heads=%d col_w=%d ldya=%d", a->rows, a->heads, a->col_w, a->ldya);
+  return cuda_status(launch_idx_q_post(*a, (cudaStream_t)stream), "idx_q_post");
+}
+
+int b200mono_index_score(const B200IndexScoreArgs* a, void* stream) {
+  REQUIRE(a && a->q_rec && a->w && a->idx_cache && a->page_table && a->req_of_row && a->ctx_len && a->scores,
+          "index_score: null pointer");
+  REQUIRE(a->rows >= 1 && a->max_pages >= 1 && a->max_ctx >= 1 && a->max_ctx <= a->max_pages * 64 &&
+              a->score_stride >= a->max_ctx,
+          "index_score: rows=%d max_pages=%d max_ctx=%d score_stride=%d", a->rows, a->max_pages, a->max_ctx,
+          a->score_stride);
+  REQUIRE(aligned(a->q_rec, 4) && aligned(a->idx_cache, 16), "index_score: q_rec 4-byte, idx_cache 16-byte aligned");
+  return cuda_status(launch_index_score(*a, (cudaStream_t)stream), "index_score");
+}
+
+int b200mono_topk(const B200TopkArgs* a, void* stream) {
+  REQUIRE(a && a->scores && a->ctx_len && a->topk_idx && a->topk_count, "topk: null pointer");
+  REQUIRE(a->rows >= 1 && a->k >= 1 && a->k <= 65535 && a->score_stride >= 1, "topk: rows=%d k=%d", a->rows, a->k);
+  return cuda_status(launch_topk(*a, (cudaStream_t)stream), "topk");
+}
+
+int b200mono_sparse_mla(const B200SparseMlaArgs* a, void* stream) {
+  REQUIRE(a && a->q_lat && a->q_rope && a->kv_cache && a->page_table && a->req_of_row && a->topk_idx && a->topk_count &&
+              a->part_o && a->part_ml && a->o_lat,
+          "sparse_mla: null pointer");
+  REQUIRE(a->rows >= 1 && a->k >= 1 && a->max_chunks == (a->k + 63) / 64 && a->max_pages >= 1 && a->heads >= 16 &&
+              a->heads % 16 == 0,
+          "sparse_mla: rows=%d k=%d max_chunks=%d heads=%d (a multiple of 16)", a->rows, a->k, a->max_chunks, a->heads);
+  REQUIRE(aligned(a->q_lat, 16) && aligned(a->q_rope, 16) && aligned(a->kv_cache, 16) && aligned(a->part_o, 16) &&
+              aligned(a->o_lat, 16),
+          "sparse_mla: pointers must be 16-byte aligned");
+  return cuda_status(launch_sparse_mla(*a, (cudaStream_t)stream), "sparse_mla");
 }
 
 int b200mono_moe_ffn_layout(int32_t rows, int32_t hidden, int32_t inter, int32_t experts, int32_t topk,

@@ -1,0 +1,161 @@
+// Front of the sparse-MLA attention block, after the low-rank projections:
+//   kv_write   latent record (FP8 latent + scales + RoPE'd key dims) and MXFP4 index-key record
+//              into the paged caches at the row's slot;
+//   q_post     per head: per-128 FP8 quant of the no-position part (input of the absorbed W_UK
+//              GEMV) and RoPE of the position part;
+//   idx_q_post per index head: RoPE on dims 64..127, MXFP4 quant, plus the head weights.
+// All arithmetic that fixes a stored byte is written with explicitly rounded f32 operations so the
+// CPU restatement reproduces the records bit for bit.
+#include "common.cuh"
+#include "launch.h"
+
+namespace b200mono {
+
+// GPT-J rotation of the pair (v0, v1) by (c, s): every product and the final add/sub is one f32 rounding.
+__device__ __forceinline__ void rope_pair(float v0, float v1, float c, float s, float& o0, float& o1) {
+  o0 = round_bf16(__fsub_rn(__fmul_rn(v0, c), __fmul_rn(v1, s)));
+  o1 = round_bf16(__fadd_rn(__fmul_rn(v0, s), __fmul_rn(v1, c)));
+}
+
+// MXFP4 of one 32-value group held one value per lane: returns the E2M1 code of this lane's value and the
+// group's E8M0 code.  Scale: the group max's exponent after rounding at mantissa bit 21, less 2 (clamped
+// at -127); code: round to nearest on the E2M1 grid, ties to the even code, saturating at 6.
+__device__ __forceinline__ uint32_t mxfp4_lane(float v, uint32_t& e8m0) {
+  const float amax = warp_max(fabsf(v));
+  const uint32_t bits = (__float_as_uint(amax) + 0x200000u) & 0xff800000u;
+  int unb = (int)((bits >> 23) & 0xffu) - 129;
+  if (unb < -127) unb = -127;
+  e8m0 = (uint32_t)(unb + 127);
+  // x * 2^-unb: the factor's exponent field 127 - unb lies in [1, 254]
+  const float q = __fmul_rn(v, __uint_as_float((uint32_t)(127 - unb) << 23));
+  const float a = fabsf(q);
+  // decision edges of the grid {0, .5, 1, 1.5, 2, 3, 4, 6}; an exact tie goes to the even code
+  uint32_t code = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
+  return code | (q < 0.f ? 8u : 0u);
+}
+
+// ------------------------------------------------------------------ kv_write
+// One CTA of 128 threads per row.  Warps 0..3 each quantise one 32-dim group of the index key;
+// warp 0 also copies the latent record, warp 1 rotates the key's position dims.
+__global__ __launch_bounds__(128) void kv_write_kernel(B200KvWriteArgs a) {
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int slot = a.slots[t];
+  if (slot <= 0) return;  // pad row: writes nothing
+  const int pos = a.positions[t];
+  const float* tab = a.rope_table + (size_t)pos * 64;
+  const __nv_bfloat16* ya = reinterpret_cast<const __nv_bfloat16*>(a.ya) + (size_t)t * a.ldya;
+  uint8_t* rec = reinterpret_cast<uint8_t*>(a.kv_cache) + (size_t)slot * 656;
+  if (warp == 0) {
+    reinterpret_cast<uint4*>(rec)[lane] = reinterpret_cast<const uint4*>(a.kv_q)[(size_t)t * 32 + lane];
+    if (lane == 0) reinterpret_cast<uint4*>(rec + 512)[0] = reinterpret_cast<const uint4*>(a.kv_scale)[t];
+  } else if (warp == 1) {
+    const float v0 = __bfloat162float(ya[a.col_rope + 2 * lane]), v1 = __bfloat162float(ya[a.col_rope + 2 * lane + 1]);
+    float o0, o1;
+    rope_pair(v0, v1, tab[lane], tab[32 + lane], o0, o1);
+    reinterpret_cast<uint32_t*>(rec + 528)[lane] = pack_bf16x2(o0, o1);
+  }
+  // index key: group = warp, dim = 32*warp + lane; dims 64..127 are rotated (pairs sit in neighbouring lanes)
+  float v = __bfloat162float(ya[a.col_idx + 32 * warp + lane]);
+  if (warp >= 2) {
+    const int pair = (32 * (warp - 2) + lane) >> 1;
+    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+    float o0, o1;
+    if (lane & 1) {
+      rope_pair(other, v, tab[pair], tab[32 + pair], o0, o1);
+      v = o1;
+    } else {
+      rope_pair(v, other, tab[pair], tab[32 + pair], o0, o1);
+      v = o0;
+    }
+  }
+  uint32_t e8;
+  const uint32_t code = mxfp4_lane(v, e8);
+  const uint32_t hi = __shfl_down_sync(0xffffffffu, code, 1);
+  // index page: [64 keys][64 bytes of codes] then [64 keys][4 scale bytes]
+  uint8_t* page = reinterpret_cast<uint8_t*>(a.idx_cache) + (size_t)(slot >> 6) * 4352;
+  const int in_page = slot & 63;
+  if (!(lane & 1)) page[in_page * 64 + 16 * warp + (lane >> 1)] = (uint8_t)(code | (hi << 4));
+  if (lane == 0) page[4096 + in_page * 4 + warp] = (uint8_t)e8;
+}
+
+cudaError_t launch_kv_write(const B200KvWriteArgs& a, cudaStream_t s) {
+  kv_write_kernel<<<a.rows, 128, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ q_post
+// warp per (row, head): q [rows, heads*192] bf16 -> qn_q e4m3 [rows, heads*128], qn_scale f32 [rows, heads],
+// q_rope bf16 [rows, heads*64].
+__global__ __launch_bounds__(256) void q_post_kernel(B200QPostArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (item >= a.rows * a.heads) return;
+  const int t = item / a.heads, h = item % a.heads;
+  const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(a.q) + ((size_t)t * a.heads + h) * 192;
+  const uint2 raw = reinterpret_cast<const uint2*>(q)[lane];  // 4 no-position dims
+  float y[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
+  const float amax = warp_max(fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3]))));
+  const float scale = __fdiv_rn(fmaxf(amax, 1e-10f), kFp8Max);
+  float v[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = fminf(fmaxf(__fdiv_rn(y[j], scale), -kFp8Max), kFp8Max);
+  reinterpret_cast<uint32_t*>(a.qn_q)[((size_t)t * a.heads + h) * 32 + lane] = f32x4_to_e4m3x4(v[0], v[1], v[2], v[3]);
+  if (lane == 0) a.qn_scale[(size_t)t * a.heads + h] = scale;
+  const float* tab = a.rope_table + (size_t)a.positions[t] * 64;
+  const uint32_t pr = reinterpret_cast<const uint32_t*>(q + 128)[lane];
+  float o0, o1;
+  rope_pair(bf16_lo(pr), bf16_hi(pr), tab[lane], tab[32 + lane], o0, o1);
+  reinterpret_cast<uint32_t*>(a.q_rope)[((size_t)t * a.heads + h) * 32 + lane] = pack_bf16x2(o0, o1);
+}
+
+cudaError_t launch_q_post(const B200QPostArgs& a, cudaStream_t s) {
+  const int items = a.rows * a.heads;
+  q_post_kernel<<<(items + 7) / 8, 256, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ idx_q_post
+// warp per (row, index head): qi [rows, heads*128] bf16 -> q_rec u8 [rows, heads, 68] (64 code bytes, 4 scale
+// bytes), and w f32 [rows, heads] = bf16 head weight * weight_scale.
+__global__ __launch_bounds__(256) void idx_q_post_kernel(B200IdxQPostArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (item >= a.rows * a.heads) return;
+  const int t = item / a.heads, h = item % a.heads;
+  const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(a.qi) + ((size_t)t * a.heads + h) * 128;
+  const float* tab = a.rope_table + (size_t)a.positions[t] * 64;
+  uint8_t* rec = reinterpret_cast<uint8_t*>(a.q_rec) + ((size_t)t * a.heads + h) * 68;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float v = __bfloat162float(q[32 * g + lane]);
+    if (g >= 2) {
+      const int pair = (32 * (g - 2) + lane) >> 1;
+      const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+      float o0, o1;
+      if (lane & 1) {
+        rope_pair(other, v, tab[pair], tab[32 + pair], o0, o1);
+        v = o1;
+      } else {
+        rope_pair(v, other, tab[pair], tab[32 + pair], o0, o1);
+        v = o0;
+      }
+    }
+    uint32_t e8;
+    const uint32_t code = mxfp4_lane(v, e8);
+    const uint32_t hi = __shfl_down_sync(0xffffffffu, code, 1);
+    if (!(lane & 1)) rec[16 * g + (lane >> 1)] = (uint8_t)(code | (hi << 4));
+    if (lane == 0) rec[64 + g] = (uint8_t)e8;
+  }
+  if (lane == 0) {
+    const float wv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.ya)[(size_t)t * a.ldya + a.col_w + h]);
+    a.w[(size_t)t * a.heads + h] = __fmul_rn(wv, a.weight_scale);
+  }
+}
+
+cudaError_t launch_idx_q_post(const B200IdxQPostArgs& a, cudaStream_t s) {
+  const int items = a.rows * a.heads;
+  idx_q_post_kernel<<<(items + 7) / 8, 256, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace b200mono

@@ -24,6 +24,12 @@ bool down_stream_ok(const B200MoeDownArgs& a);
 cudaError_t launch_moe_down_stream(const B200MoeDownArgs& a, void* contrib, uint32_t* status, int has_shared,
                                    int union_cap, cudaStream_t s);
 
+cudaError_t launch_kv_write(const B200KvWriteArgs& a, cudaStream_t s);
+cudaError_t launch_q_post(const B200QPostArgs& a, cudaStream_t s);
+cudaError_t launch_idx_q_post(const B200IdxQPostArgs& a, cudaStream_t s);
+cudaError_t launch_index_score(const B200IndexScoreArgs& a, cudaStream_t s);
+cudaError_t launch_topk(const B200TopkArgs& a, cudaStream_t s);
+cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s);
 cudaError_t launch_allreduce(const B200AllReduceArgs& a, cudaStream_t s);
 
 // device buffer for timeline marks (null: tracing off), set by b200mono_set_timeline

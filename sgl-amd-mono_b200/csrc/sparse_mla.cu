@@ -1,0 +1,218 @@
+// Sparse MLA decode over the selected FP8 latent entries (flash decoding, split + combine).
+//
+// Split: task = (row, chunk of 64 selected entries), all local heads (16 = one MMA M tile).
+//   gather the 64 paged records, dequantise e4m3 * scale -> bf16 into shared memory,
+//   S = Q K^T on bf16 tensor cores (k = 512 latent + 64 position dims), split-local softmax
+//   (own max m, sum l of the unrounded probabilities), P rounded to bf16, O = P V with V = the
+//   latent part, partial O stored bf16 with (m, l).
+// Combine: per (row, head) merge the chunk partials with w_c = exp(m_c - M) / sum_c l_c exp(m_c - M).
+#include "common.cuh"
+#include "launch.h"
+
+namespace b200mono {
+
+constexpr int kMlaHeads = 16, kLat = 512, kRope = 64, kChunkKeys = 64;
+constexpr int kLatStride = kLat + 8;    // bf16 elements per shared row (16-byte pad: conflict-free fragments)
+constexpr int kRopeStride = kRope + 8;
+constexpr int kQStride = kLat + kRope + 8;
+constexpr int kPStride = kChunkKeys + 8;
+
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
+struct MlaSmem {
+  __nv_bfloat16 lat[kChunkKeys][kLatStride];
+  __nv_bfloat16 rope[kChunkKeys][kRopeStride];
+  __nv_bfloat16 q[kMlaHeads][kQStride];
+  __nv_bfloat16 p[kMlaHeads][kPStride];
+  float s[kMlaHeads][kChunkKeys];
+};
+
+__global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs a) {
+  extern __shared__ __align__(16) uint8_t raw[];
+  MlaSmem& sm = *reinterpret_cast<MlaSmem*>(raw);
+  const int t = blockIdx.y, chunk = blockIdx.x, hg = blockIdx.z;  // hg: group of 16 heads
+  const int H = a.heads;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int n_sel = a.topk_count[t];
+  const int e0 = chunk * kChunkKeys;
+  if (e0 >= n_sel) return;
+  const int n_here = min(kChunkKeys, n_sel - e0);
+  const int req = a.req_of_row[t];
+  const int* pages = a.page_table + (size_t)req * a.max_pages;
+  const int* sel = a.topk_idx + (size_t)t * a.k + e0;
+
+  // ---- queries: [16][512 latent | 64 position] bf16
+  {
+    const uint4* ql = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_lat) + ((size_t)t * H + hg * kMlaHeads) * kLat);
+    for (int i = threadIdx.x; i < kMlaHeads * kLat / 8; i += 128) {
+      const int h = i / (kLat / 8), v = i % (kLat / 8);
+      *reinterpret_cast<uint4*>(&sm.q[h][v * 8]) = ql[i];
+    }
+    const uint4* qr = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_rope) + ((size_t)t * H + hg * kMlaHeads) * kRope);
+    for (int i = threadIdx.x; i < kMlaHeads * kRope / 8; i += 128) {
+      const int h = i / (kRope / 8), v = i % (kRope / 8);
+      *reinterpret_cast<uint4*>(&sm.q[h][kLat + v * 8]) = qr[i];
+    }
+  }
+  // ---- gather + dequantise: warp w takes keys 16w .. 16w+15
+  for (int j = 0; j < 16; ++j) {
+    const int key = warp * 16 + j;
+    uint4 lat16 = make_uint4(0, 0, 0, 0), rope16 = make_uint4(0, 0, 0, 0);
+    float scale = 0.f;
+    if (key < n_here) {
+      const int pos = sel[key];
+      const size_t slot = (size_t)pages[pos >> 6] * 64 + (pos & 63);
+      const uint8_t* rec = reinterpret_cast<const uint8_t*>(a.kv_cache) + slot * 656;
+      lat16 = reinterpret_cast<const uint4*>(rec)[lane];
+      scale = reinterpret_cast<const float*>(rec + 512)[lane >> 3];
+      if (lane < 8) rope16 = reinterpret_cast<const uint4*>(rec + 528)[lane];
+    }
+    const uint32_t w4[4] = {lat16.x, lat16.y, lat16.z, lat16.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+      const float2 lo = e4m3x2_to_f32x2(w4[q4] & 0xffffu), hi = e4m3x2_to_f32x2(w4[q4] >> 16);
+      o[2 * q4] = pack_bf16x2(lo.x * scale, lo.y * scale);
+      o[2 * q4 + 1] = pack_bf16x2(hi.x * scale, hi.y * scale);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(&sm.lat[key][lane * 16]);
+    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    if (lane < 8) *reinterpret_cast<uint4*>(&sm.rope[key][lane * 8]) = rope16;
+  }
+  __syncthreads();
+
+  // ---- S = Q K^T: warp w owns key tiles 2w, 2w+1 (8 keys each)
+  {
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    const int n0 = warp * 16;
+#pragma unroll 4
+    for (int k0 = 0; k0 < kLat + kRope; k0 += 16) {
+      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sm.q[g][k0 + 2 * c]);
+      const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sm.q[g + 8][k0 + 2 * c]);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sm.q[g][k0 + 2 * c + 8]);
+      const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sm.q[g + 8][k0 + 2 * c + 8]);
+      uint32_t b0, b1, b2, b3;
+      if (k0 < kLat) {
+        b0 = *reinterpret_cast<const uint32_t*>(&sm.lat[n0 + g][k0 + 2 * c]);
+        b1 = *reinterpret_cast<const uint32_t*>(&sm.lat[n0 + g][k0 + 2 * c + 8]);
+        b2 = *reinterpret_cast<const uint32_t*>(&sm.lat[n0 + 8 + g][k0 + 2 * c]);
+        b3 = *reinterpret_cast<const uint32_t*>(&sm.lat[n0 + 8 + g][k0 + 2 * c + 8]);
+      } else {
+        const int kr = k0 - kLat;
+        b0 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + g][kr + 2 * c]);
+        b1 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + g][kr + 2 * c + 8]);
+        b2 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + 8 + g][kr + 2 * c]);
+        b3 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + 8 + g][kr + 2 * c + 8]);
+      }
+      mma_bf16_16x8x16(s0, a0, a1, a2, a3, b0, b1);
+      mma_bf16_16x8x16(s1, a0, a1, a2, a3, b2, b3);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = g + ((i & 2) ? 8 : 0), col = 2 * c + (i & 1);
+      sm.s[row][n0 + col] = n0 + col < n_here ? s0[i] * a.scale : -INFINITY;
+      sm.s[row][n0 + 8 + col] = n0 + 8 + col < n_here ? s1[i] * a.scale : -INFINITY;
+    }
+  }
+  __syncthreads();
+  // ---- split-local softmax: warp w owns heads 4w .. 4w+3
+  for (int hh = 0; hh < 4; ++hh) {
+    const int h = warp * 4 + hh;
+    const float v0 = sm.s[h][lane], v1 = sm.s[h][lane + 32];
+    const float m = warp_max(fmaxf(v0, v1));
+    const float p0 = __expf(v0 - m), p1 = __expf(v1 - m);
+    float l = p0 + p1;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    sm.p[h][lane] = __float2bfloat16_rn(p0);
+    sm.p[h][lane + 32] = __float2bfloat16_rn(p1);
+    if (lane == 0) {
+      float* ml = a.part_ml + (((size_t)t * a.max_chunks + chunk) * H + hg * kMlaHeads + h) * 2;
+      ml[0] = m;
+      ml[1] = l;
+    }
+  }
+  __syncthreads();
+  // ---- O = P V: warp w owns latent dims 128w .. 128w+127 (16 tiles of 8)
+  {
+    uint32_t pa[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      pa[ks][0] = *reinterpret_cast<const uint32_t*>(&sm.p[g][ks * 16 + 2 * c]);
+      pa[ks][1] = *reinterpret_cast<const uint32_t*>(&sm.p[g + 8][ks * 16 + 2 * c]);
+      pa[ks][2] = *reinterpret_cast<const uint32_t*>(&sm.p[g][ks * 16 + 2 * c + 8]);
+      pa[ks][3] = *reinterpret_cast<const uint32_t*>(&sm.p[g + 8][ks * 16 + 2 * c + 8]);
+    }
+    __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(a.part_o) + (((size_t)t * a.max_chunks + chunk) * H + hg * kMlaHeads) * kLat;
+#pragma unroll 2
+    for (int nt = 0; nt < 16; ++nt) {
+      const int n0 = warp * 128 + nt * 8;
+      float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        // V tile [16 keys][8 dims], row-major in shared memory: transpose on load
+        uint32_t b0, b1;
+        const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&sm.lat[ks * 16 + (lane & 15)][n0]);
+        ldmatrix_x2_trans(b0, b1, addr);
+        mma_bf16_16x8x16(o, pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b0, b1);
+      }
+      *reinterpret_cast<uint32_t*>(po + (size_t)g * kLat + n0 + 2 * c) = pack_bf16x2(o[0], o[1]);
+      *reinterpret_cast<uint32_t*>(po + (size_t)(g + 8) * kLat + n0 + 2 * c) = pack_bf16x2(o[2], o[3]);
+    }
+  }
+}
+
+// grid (heads, rows), 128 threads: 4 latent dims per thread
+__global__ __launch_bounds__(128) void sparse_mla_combine_kernel(B200SparseMlaArgs a) {
+  const int h = blockIdx.x, t = blockIdx.y, H = a.heads;
+  const int n_sel = a.topk_count[t];
+  const int nch = (n_sel + kChunkKeys - 1) / kChunkKeys;
+  const float* ml = a.part_ml + ((size_t)t * a.max_chunks * H + h) * 2;
+  float M = -INFINITY;
+  for (int ch = 0; ch < nch; ++ch) M = fmaxf(M, ml[(size_t)ch * H * 2]);
+  float den = 0.f;
+  for (int ch = 0; ch < nch; ++ch) den += ml[(size_t)ch * H * 2 + 1] * __expf(ml[(size_t)ch * H * 2] - M);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const __nv_bfloat16* po = reinterpret_cast<const __nv_bfloat16*>(a.part_o) + ((size_t)t * a.max_chunks * H + h) * kLat;
+  for (int ch = 0; ch < nch; ++ch) {
+    const float w = __expf(ml[(size_t)ch * H * 2] - M);
+    const uint2 v = reinterpret_cast<const uint2*>(po + (size_t)ch * H * kLat)[threadIdx.x];
+    acc[0] += bf16_lo(v.x) * w;
+    acc[1] += bf16_hi(v.x) * w;
+    acc[2] += bf16_lo(v.y) * w;
+    acc[3] += bf16_hi(v.y) * w;
+  }
+  const float inv = den > 0.f ? 1.0f / den : 0.f;
+  uint2 o;
+  o.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+  o.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+  reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.o_lat) + ((size_t)t * H + h) * kLat)[threadIdx.x] = o;
+}
+
+cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(sparse_mla_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(MlaSmem));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  dim3 grid(a.max_chunks, a.rows, a.heads / kMlaHeads);
+  sparse_mla_split_kernel<<<grid, 128, sizeof(MlaSmem), s>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  dim3 grid2(a.heads, a.rows);
+  sparse_mla_combine_kernel<<<grid2, 128, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace b200mono

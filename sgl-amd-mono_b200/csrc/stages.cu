@@ -21,7 +21,7 @@ template <bool HAS_RES>
 __global__ __launch_bounds__(256) void norm_quant_kernel(B200NormQuantArgs a) {
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nvec = a.hidden >> 3;
-  const uint4* x = reinterpret_cast<const uint4*>(a.x) + (size_t)row * nvec;
+  const uint4* x = reinterpret_cast<const uint4*>(a.x) + (size_t)row * ((a.x_stride ? a.x_stride : a.hidden) >> 3);
   const uint4* r = HAS_RES ? reinterpret_cast<const uint4*>(a.residual) + (size_t)row * nvec : nullptr;
   const uint4* w = reinterpret_cast<const uint4*>(a.weight);
   __shared__ float warp_part[8];

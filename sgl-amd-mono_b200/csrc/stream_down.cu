@@ -358,7 +358,7 @@ cudaError_t launch_moe_down_stream(const B200MoeDownArgs& a, void* contrib, uint
   }
   down_stream_kernel<<<sms, kDownThreads, (size_t)stages * SB + fixed, s>>>(p, tm_w);
   cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  if (e != cudaSuccess || a.skip_combine) return e;
   const int slots = a.topk + (has_shared ? 1 : 0);
   const int nvec = a.rows * (a.hidden / 8);
   moe_combine_kernel<<<(nvec + 255) / 256, 256, 0, s>>>((const __nv_bfloat16*)contrib,

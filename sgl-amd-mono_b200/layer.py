@@ -1,0 +1,216 @@
+"""Host runner of one sparse-MLA FP8 MoE decoder layer on one tensor-parallel rank.
+
+The layer is split the way the reference splits it (sgl_amd_mono/deepseek_v41/spec.py:716-779,
+runner `k1` / `K2iRunner.select` / `k2`, sgl_amd_mono/deepseek_v41/gfx950/runner.py:603-856):
+
+  k1   input norm + quant, fused q_a/kv_a projection, q/kv norms, KV + index-key record write,
+       q_b, per-head quant + RoPE, absorbed W_UK, index query
+  k2i  index scores over the row's context, exact top-k
+  k2   sparse MLA over the selected entries, W_UV, o_proj, attention all-reduce + residual,
+       MoE FFN block, MoE all-reduce + residual
+
+Each part is a fixed sequence of C-ABI calls on the current stream over buffers this runner owns;
+nothing is allocated per step, so a step can be captured in a CUDA graph.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from . import cabi
+from .ffn import FfnBuild, FfnRunner, FfnWeights
+from .peer import AllReduce
+
+Q_LORA, KV_LORA, ROPE, NOPE, V_HEAD = 1536, 512, 64, 128, 128
+IDX_HEADS, IDX_DIM, TOPK_KEYS = 64, 128, 2048
+# columns of the fused q_a / kv_a projection output
+COL_KV, COL_ROPE, COL_IDX, COL_W, YA_COLS = 1536, 2048, 2112, 2240, 2304
+
+
+@dataclasses.dataclass(frozen=True)
+class LayerBuild:
+    width: int            # activation rows the buffers are sized for (1..32)
+    tp: int               # tensor-parallel size the weights were sharded for
+    hidden: int = 7168
+    heads: int = 128      # total attention heads (this rank holds heads // tp)
+    experts: int = 256
+    topk: int = 8
+    inter: int = 2048     # total expert intermediate size (this rank holds inter // tp)
+    max_ctx: int = 65536
+    eps: float = 1e-6
+    route_scale: float = 2.5
+    index_weight_scale: float = 0.125 / 8.0
+
+    @property
+    def heads_local(self) -> int:
+        return self.heads // self.tp
+
+
+@dataclasses.dataclass
+class LayerWeights:
+    """Device tensors of one rank.  FP8 matrices are e4m3 with f32 128x128 block scales."""
+
+    attn_norm: torch.Tensor   # bf16 [hidden]
+    wa: torch.Tensor          # e4m3 [2304, hidden]: q_a | kv_a | k_rope | index key | index head weights
+    wa_s: torch.Tensor
+    q_norm: torch.Tensor      # bf16 [1536]
+    kv_norm: torch.Tensor     # bf16 [512]
+    wq_b: torch.Tensor        # e4m3 [heads_local*192, 1536]
+    wq_b_s: torch.Tensor
+    w_uk: torch.Tensor        # e4m3 [heads_local*512, 128]: per head, absorbed
+    w_uk_s: torch.Tensor
+    wiq_b: torch.Tensor       # e4m3 [64*128, 1536]
+    wiq_b_s: torch.Tensor
+    w_uv: torch.Tensor        # e4m3 [heads_local*128, 512]: per head
+    w_uv_s: torch.Tensor
+    w_o: torch.Tensor         # e4m3 [hidden, heads_local*128]
+    w_o_s: torch.Tensor
+    ffn: FfnWeights
+
+
+@dataclasses.dataclass
+class Caches:
+    kv: torch.Tensor          # u8 [slots, 656]
+    idx: torch.Tensor         # u8 [pages, 4352]
+    rope_table: torch.Tensor  # f32 [max_pos, 64]
+
+
+@dataclasses.dataclass
+class Step:
+    """Per-step metadata (device int32 tensors)."""
+
+    positions: torch.Tensor   # [rows]
+    slots: torch.Tensor       # [rows] cache slot of each row's token (<= 0: pad row)
+    req_of_row: torch.Tensor  # [rows]
+    ctx_len: torch.Tensor     # [rows] keys visible to the row = position + 1
+    page_table: torch.Tensor  # [requests, max_pages]
+
+
+class LayerRunner:
+    def __init__(self, build: LayerBuild, weights: LayerWeights, caches: Caches, rank: int = 0, group=None,
+                 device="cuda", reducer: AllReduce | None = None, world: int | None = None):
+        """`world` is the number of ranks that actually exchange (default: build.tp).  world = 1 with tp > 1 runs
+        one rank's shard alone (its partial sums are not completed by peers): for kernel profiling and shard tests."""
+        self.lib = cabi.lib()
+        self.b, self.w, self.c, self.rank = build, weights, caches, rank
+        self.device = torch.device(device)
+        b, W, dev = build, build.width, self.device
+        hl = b.heads_local
+        if hl % 16:
+            raise ValueError(f"heads per rank ({hl}) must be a multiple of 16")
+        u8, bf, f32, i32 = torch.uint8, torch.bfloat16, torch.float32, torch.int32
+
+        def buf(shape, dt):
+            return torch.zeros(shape, dtype=dt, device=dev)
+
+        self.xq, self.xs = buf((W, b.hidden), u8), buf((W, b.hidden // 128), f32)
+        self.ya = buf((W, YA_COLS), bf)
+        self.qa_q, self.qa_s = buf((W, Q_LORA), u8), buf((W, Q_LORA // 128), f32)
+        self.kv_q, self.kv_s = buf((W, KV_LORA), u8), buf((W, 4), f32)
+        self.q = buf((W, hl * 192), bf)
+        self.qn_q, self.qn_s = buf((W, hl * NOPE), u8), buf((W, hl), f32)
+        self.q_rope = buf((W, hl * ROPE), bf)
+        self.q_lat = buf((W, hl * KV_LORA), bf)
+        self.qi = buf((W, IDX_HEADS * IDX_DIM), bf)
+        self.q_rec, self.iw = buf((W, IDX_HEADS, 68), u8), buf((W, IDX_HEADS), f32)
+        self.max_pages = (b.max_ctx + 63) // 64
+        self.scores = buf((W, self.max_pages * 64), f32)
+        self.topk_idx, self.topk_count = buf((W, TOPK_KEYS), i32), buf((W,), i32)
+        self.chunks = TOPK_KEYS // 64
+        self.part_o, self.part_ml = buf((W, self.chunks, hl, KV_LORA), bf), buf((W, self.chunks, hl, 2), f32)
+        self.o_lat = buf((W, hl * KV_LORA), bf)
+        self.ol_q, self.ol_s = buf((W, hl * KV_LORA), u8), buf((W, hl * 4), f32)
+        self.o_h = buf((W, hl * V_HEAD), bf)
+        self.oh_q, self.oh_s = buf((W, hl * V_HEAD), u8), buf((W, hl), f32)
+        self.attn_part = buf((W, b.hidden), bf)
+        self.a = buf((W, b.hidden), bf)       # residual stream after attention
+        self.status = buf((4,), i32)
+        self.ffn = FfnRunner(
+            FfnBuild(width=W, hidden=b.hidden, inter=b.inter // b.tp, experts=b.experts, topk=b.topk, score_fn=1,
+                     has_shared=True, route_scale=b.route_scale, eps=b.eps), weights.ffn, dev)
+        # one exchange buffer serves both all-reduces of the layer (and every layer of a stack):
+        # consecutive exchanges alternate between its two parity halves
+        self.reducer = reducer or AllReduce(W, b.hidden, rank if (world or b.tp) > 1 else 0, world or b.tp, group=group,
+                                            device=dev)
+
+    # ------------------------------------------------------------------ helpers
+    def _gemv(self, w, ws, xq, xs, y, rows, n, k, groups=1):
+        self.lib.call("gemv_fp8", cabi.fill("B200GemvFp8Args", w=w, w_scale=ws, xq=xq, x_scale=xs, y=y, rows=rows, n=n, k=k,
+                                            groups=groups, ldy=n, y_f32=0, status=self.status, variant=0), self._s)
+
+    def _norm_quant(self, x, weight, q, qs, rows, hidden, x_stride=0):
+        self.lib.call("norm_quant", cabi.fill("B200NormQuantArgs", x=x, weight=weight, q=q, q_scale=qs, rows=rows,
+                                              hidden=hidden, eps=self.b.eps, x_stride=x_stride), self._s)
+
+    def _quant(self, x, q, qs, rows, cols):
+        self.lib.call("quant128", cabi.fill("B200Quant128Args", x=x, q=q, q_scale=qs, rows=rows, cols=cols, zero_rule=0), self._s)
+
+    # ------------------------------------------------------------------ the three parts
+    def k1(self, x: torch.Tensor, step: Step, stream=None):
+        b, w, c, rows = self.b, self.w, self.c, x.shape[0]
+        hl = b.heads_local
+        self._s = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        self._norm_quant(x, w.attn_norm, self.xq, self.xs, rows, b.hidden)
+        self._gemv(w.wa, w.wa_s, self.xq, self.xs, self.ya, rows, YA_COLS, b.hidden)
+        self._norm_quant(self.ya, w.q_norm, self.qa_q, self.qa_s, rows, Q_LORA, x_stride=YA_COLS)
+        self._norm_quant(self.ya[:, COL_KV:], w.kv_norm, self.kv_q, self.kv_s, rows, KV_LORA, x_stride=YA_COLS)
+        self.lib.call("kv_write", cabi.fill("B200KvWriteArgs", kv_q=self.kv_q, kv_scale=self.kv_s, ya=self.ya,
+                                            positions=step.positions, slots=step.slots, rope_table=c.rope_table,
+                                            kv_cache=c.kv, idx_cache=c.idx, rows=rows, ldya=YA_COLS, col_rope=COL_ROPE,
+                                            col_idx=COL_IDX), self._s)
+        self._gemv(w.wq_b, w.wq_b_s, self.qa_q, self.qa_s, self.q, rows, hl * 192, Q_LORA)
+        self.lib.call("q_post", cabi.fill("B200QPostArgs", q=self.q, positions=step.positions, rope_table=c.rope_table,
+                                          qn_q=self.qn_q, qn_scale=self.qn_s, q_rope=self.q_rope, rows=rows, heads=hl), self._s)
+        self._gemv(w.w_uk, w.w_uk_s, self.qn_q, self.qn_s, self.q_lat, rows, hl * KV_LORA, NOPE, groups=hl)
+        self._gemv(w.wiq_b, w.wiq_b_s, self.qa_q, self.qa_s, self.qi, rows, IDX_HEADS * IDX_DIM, Q_LORA)
+        self.lib.call("idx_q_post", cabi.fill("B200IdxQPostArgs", qi=self.qi, ya=self.ya, positions=step.positions,
+                                              rope_table=c.rope_table, q_rec=self.q_rec, w=self.iw, rows=rows, heads=IDX_HEADS,
+                                              ldya=YA_COLS, col_w=COL_W, weight_scale=b.index_weight_scale), self._s)
+
+    def k2i(self, rows: int, step: Step, stream=None):
+        self._s = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        self.lib.call("index_score", cabi.fill("B200IndexScoreArgs", q_rec=self.q_rec, w=self.iw, idx_cache=self.c.idx,
+                                               page_table=step.page_table, req_of_row=step.req_of_row, ctx_len=step.ctx_len,
+                                               scores=self.scores, rows=rows, max_pages=step.page_table.shape[1],
+                                               max_ctx=step.page_table.shape[1] * 64, score_stride=self.scores.shape[1]), self._s)
+        self.lib.call("topk", cabi.fill("B200TopkArgs", scores=self.scores, ctx_len=step.ctx_len, topk_idx=self.topk_idx,
+                                        topk_count=self.topk_count, rows=rows, k=TOPK_KEYS,
+                                        score_stride=self.scores.shape[1]), self._s)
+
+    def k2(self, x: torch.Tensor, out: torch.Tensor, step: Step, stream=None):
+        b, w, rows = self.b, self.w, x.shape[0]
+        hl = b.heads_local
+        st = stream or torch.cuda.current_stream(self.device)
+        self._s = st.cuda_stream
+        self.lib.call("sparse_mla", cabi.fill("B200SparseMlaArgs", q_lat=self.q_lat, q_rope=self.q_rope, kv_cache=self.c.kv,
+                                              page_table=step.page_table, req_of_row=step.req_of_row, topk_idx=self.topk_idx,
+                                              topk_count=self.topk_count, part_o=self.part_o, part_ml=self.part_ml,
+                                              o_lat=self.o_lat, rows=rows, k=TOPK_KEYS, max_pages=step.page_table.shape[1],
+                                              max_chunks=self.chunks, scale=192 ** -0.5, heads=hl), self._s)
+        self._quant(self.o_lat, self.ol_q, self.ol_s, rows, hl * KV_LORA)
+        self._gemv(w.w_uv, w.w_uv_s, self.ol_q, self.ol_s, self.o_h, rows, hl * V_HEAD, KV_LORA, groups=hl)
+        self._quant(self.o_h, self.oh_q, self.oh_s, rows, hl * V_HEAD)
+        self._gemv(w.w_o, w.w_o_s, self.oh_q, self.oh_s, self.attn_part, rows, b.hidden, hl * V_HEAD)
+        a = self.a[:rows]
+        self.reducer.run(self.attn_part[:rows], x, a, stream=st)
+        # MoE block on the reduced stream; its slot-ordered combine is fused into the second all-reduce
+        calls = self.ffn.stage_calls(a, out, None, False)
+        for name, args in calls[:-1]:
+            self.lib.call(name, args, self._s)
+        name, dn = calls[-1]
+        dn.variant = 2
+        dn.skip_combine = 1  # the all-reduce sums the slots
+        self.lib.call(name, dn, self._s)
+        L = self.ffn.step_layout
+        slots = b.topk + 1
+        contrib = self.ffn.scratch[L.contrib: L.contrib + slots * rows * b.hidden * 2].view(torch.bfloat16).view(
+            slots, rows, b.hidden)
+        self.reducer.run(contrib, a, out, slots=slots, stream=st)
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, step: Step, stream=None):
+        self.k1(x, step, stream)
+        self.k2i(x.shape[0], step, stream)
+        self.k2(x, out, step, stream)
+        return out

@@ -1,0 +1,30 @@
+"""The plugin entry point a serving engine runs in every process (`sglang.srt.plugins` entry-point group),
+the counterpart of sgl_amd_mono/__init__.py:64-79: it registers each (architecture, model type) spec under this
+backend's name; the spec modules import lazily, only when a server runs the backend."""
+
+from __future__ import annotations
+
+BACKEND = "b200"
+ISA = "sm_100a"
+# each spec by (HF architecture, model type); None = any model type
+SPECS = {
+    ("DeepseekV32ForCausalLM", None): "sgl_amd_mono_b200.sparse_mla_moe.spec:SPEC",
+    ("GlmMoeDsaForCausalLM", None): "sgl_amd_mono_b200.sparse_mla_moe.spec:SPEC",
+}
+
+
+def _register_fn():
+    try:  # the engine's own interface when it is installed
+        from sglang.kernels.plugin_kernels.amd.spec import register  # type: ignore
+
+        return register
+    except ModuleNotFoundError:
+        from .spec_api import register
+
+        return register
+
+
+def register_specs() -> None:
+    register = _register_fn()
+    for (architecture, model_type), path in SPECS.items():
+        register(backend=BACKEND, architecture=architecture, path=path, model_type=model_type)

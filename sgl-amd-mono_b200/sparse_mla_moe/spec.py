@@ -1,0 +1,124 @@
+"""Spec of the sparse-MLA FP8 MoE model family: what the launches support, why they may refuse a model or a
+server configuration, how a model is built into per-layer runners, and the routed forward.
+
+Mirrors sgl_amd_mono/deepseek_v41/spec.py (SPEC at :1259-1310, `_build` at :1211-1256, the routed
+`_Built.forward` at :945-971) and the routing rule of sgl_amd_mono/qwen35_a17b/fp8/spec.py:421-436: a step is served
+by the launches or by the model's own forward depending on the CUDA-graph shape key alone, so every rank takes the
+same decision and a captured graph replays it.
+"""
+
+from __future__ import annotations
+
+import logging
+
+import torch
+
+from ..layer import Caches, LayerBuild, LayerRunner, LayerWeights, Step
+from ..spec_api import DeviceLimits, Feature, MonoSpec, Numerics, NumericsKind, Plan, Requirements
+
+log = logging.getLogger(__name__)
+
+MAX_ROWS = 32
+ROUTED_MODES = ("decode", "target_verify")
+HF_CONFIG = dict(hidden_size=7168, num_attention_heads=128, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+                 qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=256, num_experts_per_tok=8, moe_intermediate_size=2048,
+                 n_shared_experts=1, index_n_heads=64, index_head_dim=128, index_topk=2048)
+
+# bounds the check mode and the kernel tests hold the launches to (cf. NUMERICS, sgl_amd_mono/deepseek_v41/spec.py:335-363)
+NUMERICS = Numerics(NumericsKind.TOLERANCE, {
+    "k1.kv.max_abs": 0.0, "k1.index_key.max_abs": 0.0, "k1.q.rel": 5e-3, "k2i.logits.max_abs": 0.0, "k2i.sel.max_abs": 0.0,
+    "k2.attn_out.rel": 1e-2, "k2.wo.rel": 1e-2, "ffn.routing.max_abs": 0.0, "ffn.moe.rel": 2e-2, "layer.hidden.rel": 2e-2,
+})
+
+
+def _config_disable_reasons(cfg, hf_config) -> list[str]:
+    """Reasons this server configuration cannot be served (empty list = fine)."""
+    why = []
+    tp = getattr(cfg, "tp_size", 1)
+    if tp not in (1, 2, 4, 8):
+        why.append(f"tensor parallel size {tp} is not one of 1, 2, 4, 8")
+    if getattr(cfg, "ep_size", 1) != 1:
+        why.append("expert parallelism is not built (every rank holds a slice of every expert)")
+    if getattr(cfg, "kv_cache_dtype", "fp8_e4m3") != "fp8_e4m3":
+        why.append(f"kv_cache_dtype {getattr(cfg, 'kv_cache_dtype', None)!r}: the launches read the 656-byte FP8 latent records")
+    if getattr(cfg, "page_size", 64) != 64:
+        why.append(f"page size {getattr(cfg, 'page_size', None)}: the caches are walked in 64-token pages")
+    return why
+
+
+def _model_disable_reasons(model, hf_config, copies=None) -> list[str]:
+    """Reasons this checkpoint cannot be served."""
+    why = []
+    for key, want in HF_CONFIG.items():
+        got = getattr(hf_config, key, None) if not isinstance(hf_config, dict) else hf_config.get(key)
+        if got != want:
+            why.append(f"hf_config.{key} = {got!r}, the launches are built for {want!r}")
+    q = getattr(hf_config, "quantization_config", None) if not isinstance(hf_config, dict) else hf_config.get("quantization_config")
+    if not q or q.get("quant_method") != "fp8" or list(q.get("weight_block_size", [])) != [128, 128]:
+        why.append("weights must be FP8 e4m3 with 128x128 block scales")
+    return why
+
+
+class _Built:
+    """What `build` returns: one runner per layer and the routed forward."""
+
+    def __init__(self, model, layers: list[LayerRunner], widths: tuple[int, ...]):
+        self.model, self.layers, self.widths = model, layers, widths
+
+    def routes(self, key) -> bool:
+        """Routing depends on the graph shape key only."""
+        return key.forward_mode in ROUTED_MODES and 1 <= key.rows <= max(self.widths) and key.rows in self.widths
+
+    def forward(self, plan: Plan, input_ids, positions, forward_batch, input_embeds=None, *more):
+        if not self.routes(plan.key):
+            return type(self.model).forward(self.model, input_ids, positions, forward_batch, input_embeds, *more)
+        x = self.model.embed(input_ids) if input_embeds is None else input_embeds
+        step = Step(positions=positions.to(torch.int32), slots=forward_batch.out_cache_loc.to(torch.int32),
+                    req_of_row=forward_batch.req_of_row, ctx_len=(positions + 1).to(torch.int32),
+                    page_table=forward_batch.page_table)
+        out = plan.state.setdefault("out", torch.empty_like(x))
+        for runner in self.layers:
+            runner.forward(x, out, step)
+            x, out = out, x
+        plan.state["out"] = out
+        return self.model.head(x, forward_batch)
+
+
+def _build(model, hf_config, ctx) -> _Built:
+    """Per-layer weight views and runners; collective across ranks (the peer-buffer handshake).  Nothing may be
+    built later, inside graph capture."""
+    layers = []
+    tp, rank = getattr(ctx, "tp_size", 1), getattr(ctx, "tp_rank", 0)
+    width = max(ctx.widths)
+    reducer = None
+    for i, lw in enumerate(model.layer_weights()):  # LayerWeights per layer, tensors read in place
+        assert isinstance(lw, LayerWeights)
+        caches: Caches = model.layer_caches(i)
+        b = LayerBuild(width=width, tp=tp)
+        r = LayerRunner(b, lw, caches, rank=rank, group=getattr(ctx, "cpu_group", None), device=ctx.device, reducer=reducer)
+        reducer = r.reducer  # one exchange buffer for the whole stack
+        layers.append(r)
+    log.info("sparse_mla_moe: %d layers served by K1/K2i/K2 launches for %s steps of 1..%d rows", len(layers),
+             "/".join(ROUTED_MODES), width)
+    return _Built(model, layers, tuple(ctx.widths))
+
+
+SPEC = MonoSpec(
+    name="sparse_mla_moe_b200",
+    devices={"sm_100a": DeviceLimits(widths=tuple(range(1, MAX_ROWS + 1)), tp_sizes=(1, 2, 4, 8), resident_blocks=148)},
+    features=frozenset({Feature.SPECULATIVE_DECODING}),
+    requires=Requirements(
+        dtypes=frozenset({"bfloat16"}),
+        attention_backends=frozenset({"nsa", "dsa"}),
+        server_args={"kv_cache_dtype": frozenset({"fp8_e4m3"}), "page_size": frozenset({64})},
+        hf_config=dict(HF_CONFIG),
+        env={},
+    ),
+    numerics=NUMERICS,
+    model_disable_reasons=_model_disable_reasons,
+    build=_build,
+    api_version=1,
+    config_disable_reasons=_config_disable_reasons,
+    load_tensor=None,
+    unread_metadata=frozenset(),
+)

@@ -1,0 +1,217 @@
+"""GPU parity of the sparse-MLA attention side through the C ABI against the oracle: cache records
+bit-exact, index scores bit-exact, top-k exact (adversarial ties included), attention within tolerance."""
+
+import numpy as np
+import pytest
+import torch
+
+import sgl_amd_mono_b200  # noqa: F401
+from oracle import attn as A
+from oracle import moe as M
+from oracle import quant as Q
+from sgl_amd_mono_b200 import cabi
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def rel(a, b):
+    a, b = a.detach().cpu().double().reshape(-1), b.detach().cpu().double().reshape(-1)
+    return ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+def test_kv_and_index_records_bit_exact(lib):
+    rows, ldya, eps = 6, 2304, 1e-6
+    g = torch.Generator().manual_seed(1)
+    ya = (torch.randn(rows, ldya, generator=g) * 2).bfloat16()
+    ya[2, 2112:2144] = 0  # an all-zero index group: scale code 0
+    wkv = (1 + 0.1 * torch.randn(512, generator=g)).bfloat16()
+    pos = torch.tensor([0, 5, 4095, 17, 65535, 9], dtype=torch.int32)
+    slots = torch.tensor([64 + 3, 64 * 7 + 63, 0, 64 * 2, -1, 64 * 9 + 1], dtype=torch.int32)  # rows 2 and 4 are pad rows
+    table = A.rope_table(65536)
+    n_pages = 12
+    kv_cache = torch.full((n_pages * 64, 656), 0xAA, dtype=torch.uint8, device=DEV)
+    idx_cache = torch.full((n_pages, 4352), 0xAA, dtype=torch.uint8, device=DEV)
+    yad, wd = ya.to(DEV), wkv.to(DEV)
+    kv_q = torch.zeros(rows, 512, dtype=torch.uint8, device=DEV)
+    kv_s = torch.zeros(rows, 4, device=DEV)
+    lib.call("norm_quant", cabi.fill("B200NormQuantArgs", x=yad[:, 1536:], weight=wd, q=kv_q, q_scale=kv_s, rows=rows,
+                                     hidden=512, eps=eps, x_stride=ldya), stream())
+    lib.call("kv_write", cabi.fill("B200KvWriteArgs", kv_q=kv_q, kv_scale=kv_s, ya=yad, positions=pos.to(DEV),
+                                   slots=slots.to(DEV), rope_table=table.to(DEV), kv_cache=kv_cache, idx_cache=idx_cache,
+                                   rows=rows, ldya=ldya, col_rope=2048, col_idx=2112), stream())
+    torch.cuda.synchronize()
+    _, _, q_ref, s_ref = M.rmsnorm_quant(ya[:, 1536:2048].contiguous(), wkv, eps)
+    assert torch.equal(kv_q.cpu(), q_ref.view(torch.uint8)) and torch.equal(kv_s.cpu(), s_ref)
+    rec_ref = A.kv_record(q_ref, s_ref, A.rope_gptj(ya[:, 2048:2112].contiguous(), pos, table))
+    k = ya[:, 2112:2240].clone()
+    k[:, 64:] = A.rope_gptj(k[:, 64:].contiguous(), pos, table)
+    idx_ref = A.index_record(k)
+    kvc, idc = kv_cache.cpu(), idx_cache.cpu()
+    live = [t for t in range(rows) if int(slots[t]) > 0]
+    for t in live:
+        s = int(slots[t])
+        assert torch.equal(kvc[s], rec_ref[t]), f"KV record of row {t}"
+        page, e = idc[s // 64], s % 64
+        assert torch.equal(page[e * 64:e * 64 + 64], idx_ref[t, :64]), f"index codes of row {t}"
+        assert torch.equal(page[4096 + e * 4:4096 + e * 4 + 4], idx_ref[t, 64:]), f"index scales of row {t}"
+    # nothing else was touched (pad rows write nothing, live rows only their own slot)
+    kvc2, idc2 = kvc.clone(), idc.clone()
+    for t in live:
+        s = int(slots[t])
+        kvc2[s] = 0xAA
+        idc2[s // 64, (s % 64) * 64:(s % 64) * 64 + 64] = 0xAA
+        idc2[s // 64, 4096 + (s % 64) * 4:4096 + (s % 64) * 4 + 4] = 0xAA
+    assert bool((kvc2 == 0xAA).all()) and bool((idc2 == 0xAA).all())
+
+
+def test_q_post_and_index_query_bit_exact(lib):
+    rows, heads, iheads, ldya = 5, 16, 64, 2304
+    g = torch.Generator().manual_seed(2)
+    q = (torch.randn(rows, heads * 192, generator=g) * 1.5).bfloat16()
+    qi = (torch.randn(rows, iheads * 128, generator=g) * 3).bfloat16()
+    ya = torch.randn(rows, ldya, generator=g).bfloat16()
+    pos = torch.tensor([3, 100, 4096, 65000, 0], dtype=torch.int32)
+    table = A.rope_table(65536)
+    qn_q = torch.zeros(rows, heads * 128, dtype=torch.uint8, device=DEV)
+    qn_s = torch.zeros(rows, heads, device=DEV)
+    q_rope = torch.zeros(rows, heads * 64, dtype=torch.bfloat16, device=DEV)
+    lib.call("q_post", cabi.fill("B200QPostArgs", q=q.to(DEV), positions=pos.to(DEV), rope_table=table.to(DEV), qn_q=qn_q,
+                                 qn_scale=qn_s, q_rope=q_rope, rows=rows, heads=heads), stream())
+    q_rec = torch.zeros(rows, iheads, 68, dtype=torch.uint8, device=DEV)
+    w = torch.zeros(rows, iheads, device=DEV)
+    lib.call("idx_q_post", cabi.fill("B200IdxQPostArgs", qi=qi.to(DEV), ya=ya.to(DEV), positions=pos.to(DEV),
+                                     rope_table=table.to(DEV), q_rec=q_rec, w=w, rows=rows, heads=iheads, ldya=ldya,
+                                     col_w=2240, weight_scale=0.125), stream())
+    torch.cuda.synchronize()
+    qh = q.view(rows, heads, 192)
+    qq, qs = Q.quant128(qh[:, :, :128].contiguous())
+    assert torch.equal(qn_q.cpu().view(rows, heads, 128), qq.view(torch.uint8)) and torch.equal(qn_s.cpu(), qs.squeeze(-1))
+    assert torch.equal(q_rope.cpu().view(rows, heads, 64).view(torch.int16),
+                       A.rope_gptj(qh[:, :, 128:].contiguous(), pos, table).view(torch.int16))
+    qih = qi.view(rows, iheads, 128).clone()
+    qih[:, :, 64:] = A.rope_gptj(qih[:, :, 64:].contiguous(), pos, table)
+    assert torch.equal(q_rec.cpu(), A.index_record(qih.reshape(rows * iheads, 128)).view(rows, iheads, 68))
+    assert torch.equal(w.cpu(), ya[:, 2240:2304].float() * 0.125)
+
+
+def _index_case(rows, ctx, seed, reqs=None):
+    """Random query records, random key pages behind a permuted page table."""
+    g = torch.Generator().manual_seed(seed)
+    reqs = reqs or list(range(rows))
+    n_req = max(reqs) + 1
+    max_pages = (max(ctx) + 63) // 64
+    n_pages = n_req * max_pages + 1
+    q_rec = torch.randint(0, 256, (rows, 64, 68), generator=g, dtype=torch.uint8)
+    q_rec[:, :, 64:] = torch.randint(118, 131, (rows, 64, 4), generator=g, dtype=torch.uint8)
+    w = torch.randn(rows, 64, generator=g) * 0.1
+    cache = torch.randint(0, 256, (n_pages, 4352), generator=g, dtype=torch.uint8)
+    cache[:, 4096:] = torch.randint(118, 131, (n_pages, 256), generator=g, dtype=torch.uint8)
+    perm = torch.randperm(n_pages - 1, generator=g)[: n_req * max_pages] + 1  # page 0 is the pad page
+    table = perm.view(n_req, max_pages).to(torch.int32)
+    return q_rec, w, cache, table, max_pages
+
+
+def _keys_of(cache, table, req, n):
+    pages = cache[table[req, : (n + 63) // 64].long()]
+    codes = pages[:, :4096].reshape(-1, 64)[:n]
+    scales = pages[:, 4096:].reshape(-1, 4)[:n]
+    return torch.cat([codes, scales], 1)
+
+
+@pytest.mark.parametrize("ctx", [[17, 64, 65, 1000], [4096, 5000, 1, 2047, 2048, 2049, 9000, 300], [65536, 40000]])
+def test_index_scores_bit_exact(lib, ctx):
+    rows = len(ctx)
+    q_rec, w, cache, table, max_pages = _index_case(rows, ctx, seed=rows)
+    stride = max_pages * 64
+    scores = torch.full((rows, stride), float("nan"), device=DEV)
+    lib.call("index_score", cabi.fill("B200IndexScoreArgs", q_rec=q_rec.to(DEV), w=w.to(DEV), idx_cache=cache.to(DEV),
+                                      page_table=table.to(DEV), req_of_row=i32(list(range(rows))), ctx_len=i32(ctx),
+                                      scores=scores, rows=rows, max_pages=max_pages, max_ctx=max(ctx), score_stride=stride),
+             stream())
+    torch.cuda.synchronize()
+    got = scores.cpu().numpy()
+    for t in range(rows):
+        ref = A.index_scores(q_rec[t], w[t], _keys_of(cache, table, t, ctx[t]))
+        assert np.array_equal(got[t, : ctx[t]].view(np.uint32), ref.view(np.uint32)), f"row {t}"
+        assert np.isnan(got[t, ctx[t]:]).all(), "wrote past the row's context"
+
+
+def test_topk_exact_with_adversarial_scores(lib):
+    k = 2048
+    g = torch.Generator().manual_seed(7)
+    cases = [
+        torch.randn(65536, generator=g),
+        torch.zeros(5000),                                     # all equal: the first k positions
+        torch.randn(3000, generator=g).round(),                # heavy ties
+        torch.cat([torch.full((3000,), -1.0), torch.full((100,), 2.0), torch.full((3000,), -1.0)]),
+        torch.randn(2048, generator=g), torch.randn(2049, generator=g), torch.randn(17, generator=g),
+        torch.cat([torch.zeros(4000), -torch.zeros(4000)]),    # +0 and -0 are different keys
+        torch.randn(40000, generator=g).abs() * 1e-30,         # tiny values: high bytes all equal
+        -torch.rand(10000, generator=g),
+    ]
+    rows = len(cases)
+    stride = 65536
+    scores = torch.full((rows, stride), float("nan"))
+    for t, cse in enumerate(cases):
+        scores[t, : len(cse)] = cse
+    ctx = [len(cse) for cse in cases]
+    idx = torch.full((rows, k), -1, dtype=torch.int32, device=DEV)
+    cnt = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    lib.call("topk", cabi.fill("B200TopkArgs", scores=scores.to(DEV), ctx_len=i32(ctx), topk_idx=idx, topk_count=cnt,
+                               rows=rows, k=k, score_stride=stride), stream())
+    torch.cuda.synchronize()
+    for t, cse in enumerate(cases):
+        ref = A.exact_topk(cse.numpy(), k)
+        n = int(cnt[t].item())
+        assert n == len(ref), f"case {t}"
+        assert np.array_equal(idx[t, :n].cpu().numpy(), ref), f"case {t}"
+    # negative control: swapping two selected entries must be caught by the comparison above
+    ref = A.exact_topk(cases[0].numpy(), k)
+    bad = idx[0, : len(ref)].cpu().numpy().copy()
+    bad[[0, 1]] = bad[[1, 0]]
+    assert not np.array_equal(bad, ref)
+
+
+@pytest.mark.parametrize("n_sel", [[2048, 2048, 100, 65], [64, 1, 2047, 1000, 2048, 2048, 2048, 2048]])
+def test_sparse_mla_against_oracle(lib, n_sel):
+    rows, k = len(n_sel), 2048
+    g = torch.Generator().manual_seed(rows)
+    ctx = [max(n, 5000) for n in n_sel]
+    max_pages = (max(ctx) + 63) // 64
+    n_pages = rows * max_pages + 1
+    cache = torch.randint(0, 256, (n_pages * 64, 656), generator=g, dtype=torch.uint8)
+    lat = cache[:, :512]
+    lat[(lat & 0x7f) == 0x7f] = 0x38  # no NaN codes
+    cache[:, 512:528] = (torch.rand(n_pages * 64, 4, generator=g) * 0.02 + 0.001).view(torch.uint8).reshape(-1, 16)
+    cache[:, 528:] = torch.randn(n_pages * 64, 64, generator=g).bfloat16().view(torch.uint8).reshape(-1, 128)
+    table = (torch.randperm(n_pages - 1, generator=g)[: rows * max_pages] + 1).view(rows, max_pages).to(torch.int32)
+    q_lat = (torch.randn(rows, 16, 512, generator=g) * 0.3).bfloat16()
+    q_rope = (torch.randn(rows, 16, 64, generator=g) * 0.3).bfloat16()
+    sel = torch.zeros(rows, k, dtype=torch.int32)
+    for t in range(rows):
+        sel[t, : n_sel[t]] = torch.sort(torch.randperm(ctx[t], generator=g)[: n_sel[t]]).values.to(torch.int32)
+    scale = 192 ** -0.5
+    chunks = k // 64
+    part_o = torch.full((rows, chunks, 16, 512), float("nan"), dtype=torch.bfloat16, device=DEV)
+    part_ml = torch.full((rows, chunks, 16, 2), float("nan"), device=DEV)
+    o = torch.full((rows, 16, 512), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lib.call("sparse_mla", cabi.fill("B200SparseMlaArgs", q_lat=q_lat.to(DEV), q_rope=q_rope.to(DEV), kv_cache=cache.to(DEV),
+                                     page_table=table.to(DEV), req_of_row=i32(list(range(rows))), topk_idx=sel.to(DEV),
+                                     topk_count=i32(n_sel), part_o=part_o, part_ml=part_ml, o_lat=o, rows=rows, k=k,
+                                     max_pages=max_pages, max_chunks=chunks, scale=scale, heads=16), stream())
+    torch.cuda.synchronize()
+    for t in range(rows):
+        pos = sel[t, : n_sel[t]].long()
+        slots = table[t, pos // 64].long() * 64 + pos % 64
+        ref = A.sparse_mla(q_lat[t], q_rope[t], cache[slots], scale)
+        e = rel(o[t], ref)
+        assert e < 1e-2, (t, e)  # bf16 output of an FP8-cache attention; differences: exp and summation order

@@ -1,0 +1,92 @@
+"""The whole sparse-MLA FP8 MoE decoder layer through the host runner (K1, K2i, K2) against the oracle.
+
+Stage checks consume the launch's own intermediates (records, scores, selections bit-exact; GEMV-fed values within
+tolerance); the end-to-end check compares the layer output with the oracle run from the same inputs."""
+
+import numpy as np
+import pytest
+import torch
+
+import sgl_amd_mono_b200  # noqa: F401
+from oracle import attn as A
+from oracle import collective as C
+from oracle import layer as L
+from sgl_amd_mono_b200.ffn import FfnWeights
+from sgl_amd_mono_b200.layer import Caches, LayerBuild, LayerRunner, LayerWeights, Step
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel(a, b):
+    a, b = a.detach().cpu().double().reshape(-1), b.detach().cpu().double().reshape(-1)
+    return ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+
+
+def build_runner(cfg, w, caches, width):
+    lw = LayerWeights(
+        attn_norm=w["attn_norm"], wa=w["wa"], wa_s=w["wa_s"], q_norm=w["q_norm"], kv_norm=w["kv_norm"], wq_b=w["wq_b"],
+        wq_b_s=w["wq_b_s"], w_uk=w["w_uk"], w_uk_s=w["w_uk_s"], wiq_b=w["wiq_b"], wiq_b_s=w["wiq_b_s"], w_uv=w["w_uv"],
+        w_uv_s=w["w_uv_s"], w_o=w["w_o"], w_o_s=w["w_o_s"],
+        ffn=FfnWeights(norm=w["ffn_norm"], gate_w=w["gate_w"], bias=w["bias"], w13=w["w13"], w13_s=w["w13_s"], w2=w["w2"],
+                       w2_s=w["w2_s"]))
+    b = LayerBuild(width=width, tp=cfg["tp"], hidden=cfg["hidden"], heads=cfg["heads"], experts=cfg["experts"],
+                   topk=cfg["topk"], inter=cfg["inter"], max_ctx=cfg["max_ctx"])
+    return LayerRunner(b, lw, Caches(kv=caches["kv"], idx=caches["idx"], rope_table=caches["rope_table"]), device=DEV, world=1)
+
+
+@pytest.mark.parametrize("rows,tokens_per_request,ctx", [(4, 1, (4096, 9000)), (8, 4, (2040, 2060)), (3, 1, (1, 300))])
+def test_layer_shard_against_oracle(lib, rows, tokens_per_request, ctx):
+    # rank 0's shard of the TP8 layer (16 heads, expert slices of 256) run alone
+    cfg = L.layer_cfg(tp=8, experts=64, max_ctx=16384)
+    w = L.make_weights(cfg, rank=0, seed=1, device=DEV)
+    caches, step = L.make_step(cfg, rows, ctx[0], ctx[1], seed=rows, tokens_per_request=tokens_per_request, device=DEV)
+    cpu_caches0 = {k: v.cpu().clone() for k, v in caches.items()}
+    x = torch.randn(rows, cfg["hidden"], generator=torch.Generator().manual_seed(rows)).bfloat16().to(DEV)
+    r = build_runner(cfg, w, caches, rows)
+    out = torch.full_like(x, float("nan"))
+    st = Step(**step)
+    r.forward(x, out, st)
+    torch.cuda.synchronize()
+    assert r.reducer.status() == 0 and r.ffn.status() == 0 and int(r.status[0].item()) == 0
+    cs = {k: v.cpu() for k, v in step.items()}
+
+    # ---- K1: records and queries from the launch's own projections
+    f = L.k1_from_ya(r.ya[:rows], w, cpu_caches0, cs, cfg, q=r.q[:rows], qi=r.qi[:rows])
+    ref_caches = {k: v.clone() for k, v in cpu_caches0.items()}
+    L.write_records(ref_caches, cs, f["kv_rec"], f["idx_rec"])
+    assert torch.equal(caches["kv"].cpu(), ref_caches["kv"]), "KV cache bytes"
+    assert torch.equal(caches["idx"].cpu(), ref_caches["idx"]), "index cache bytes"
+    assert torch.equal(r.q_rec[:rows].cpu(), f["q_rec"]) and torch.equal(r.iw[:rows].cpu(), f["iw"])
+    assert torch.equal(r.q_rope[:rows].cpu().view(torch.int16), f["q_rope"].view(torch.int16))
+    assert rel(r.q_lat[:rows], f["q_lat"]) < 5e-3
+    ya_ref = L.k1(x, w, {k: v.clone() for k, v in cpu_caches0.items()}, cs, cfg)["ya"]
+    assert rel(r.ya[:rows], ya_ref) < 5e-3
+
+    # ---- K2i: scores and selection from the launch's own query records and caches
+    sel = L.k2i(r.q_rec[:rows].cpu(), r.iw[:rows].cpu(), ref_caches, cs)
+    got_scores = r.scores[:rows].cpu().numpy()
+    for t, (s, idx) in enumerate(sel):
+        n = int(cs["ctx_len"][t])
+        assert np.array_equal(got_scores[t, :n].view(np.uint32), s.view(np.uint32)), f"scores of row {t}"
+        k = int(r.topk_count[t].item())
+        assert k == len(idx) and np.array_equal(r.topk_idx[t, :k].cpu().numpy(), idx), f"selection of row {t}"
+
+    # ---- K2: attention, projections, exchanges
+    o_ref = L.attention(r.q_lat[:rows], r.q_rope[:rows], [i for _, i in sel], ref_caches, cs, cfg)
+    assert rel(r.o_lat[:rows], o_ref) < 1e-2
+    part_ref, _ = L.attn_out_partial(r.o_lat[:rows], w, cfg)
+    assert rel(r.attn_part[:rows], part_ref) < 1e-2
+    assert torch.equal(r.a[:rows].cpu(), C.allreduce([r.attn_part[:rows]], x)), "residual stream after attention"
+    ffn_ref = L.ffn_contrib(r.a[:rows], w, cfg)
+    Lay = r.ffn.step_layout
+    ids = r.ffn.scratch[Lay.topk_ids: Lay.topk_ids + rows * cfg["topk"] * 4].view(torch.int32).view(rows, cfg["topk"]).cpu().numpy()
+    assert np.array_equal(ids, ffn_ref["ids"]), "routing"
+    assert rel(out, C.allreduce([ffn_ref["out"]], r.a[:rows])) < 2e-2
+
+    # ---- end to end from the same inputs
+    ref = L.forward(x, [w], cpu_caches0, cs, cfg)
+    e = rel(out, ref["out"])
+    assert e < 2e-2, e
+    # rows are independent of each other: a verify row sees its earlier siblings through the cache only
+    assert not torch.isnan(out.float()).any()

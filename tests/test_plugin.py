@@ -1,0 +1,95 @@
+"""The plugin surface: entry point, lazy spec registration, lookup, refusal reasons and graph-key routing, with
+fake models and configs (SimpleNamespace), as the reference tests its specs
+(test/unit/test_deepseek_v41_spec.py:44-134, test/unit/test_deepseek_v4_spec.py:43-62)."""
+
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import sgl_amd_mono_b200  # noqa: F401
+from sgl_amd_mono_b200 import plugin, spec_api
+from sgl_amd_mono_b200.spec_api import Plan, ShapeKey
+
+
+@pytest.fixture(autouse=True)
+def fresh_registry():
+    spec_api.clear_registry()
+    yield
+    spec_api.clear_registry()
+
+
+def test_entry_point_registers_every_spec_lazily():
+    assert not spec_api.spec_registered(plugin.BACKEND, "GlmMoeDsaForCausalLM")
+    plugin.register_specs()
+    for (arch, mt) in plugin.SPECS:
+        assert spec_api.spec_registered(plugin.BACKEND, arch, mt)
+    spec, why = spec_api.find_spec(plugin.BACKEND, ["SomethingElse", "DeepseekV32ForCausalLM"], "sm_100a")
+    assert spec is not None and why == "" and spec.name == "sparse_mla_moe_b200"
+    assert spec.api_version == spec_api.MONOKERNEL_API_VERSION
+    lim = spec.devices["sm_100a"]
+    assert lim.tp_sizes == (1, 2, 4, 8) and lim.widths == tuple(range(1, 33)) and lim.resident_blocks == 148
+
+
+def test_lookup_failures_say_why():
+    plugin.register_specs()
+    spec, why = spec_api.find_spec(plugin.BACKEND, ["LlamaForCausalLM"], "sm_100a")
+    assert spec is None and "LlamaForCausalLM" in why
+    spec, why = spec_api.find_spec(plugin.BACKEND, ["GlmMoeDsaForCausalLM"], "gfx950")
+    assert spec is None and "gfx950" in why
+    spec, why = spec_api.find_spec("amd", ["GlmMoeDsaForCausalLM"], "sm_100a")
+    assert spec is None
+    with pytest.raises(ValueError):
+        spec_api.register("b200", "X", "not_a_path")
+
+
+def test_refusal_reasons_list_every_problem():
+    from sgl_amd_mono_b200.sparse_mla_moe.spec import HF_CONFIG, SPEC
+
+    good = dict(HF_CONFIG, quantization_config={"quant_method": "fp8", "weight_block_size": [128, 128]})
+    assert SPEC.model_disable_reasons(None, good) == []
+    bad = dict(good, hidden_size=4096, index_topk=1024, quantization_config={"quant_method": "awq"})
+    why = SPEC.model_disable_reasons(None, bad)
+    assert len(why) == 3 and any("hidden_size" in w for w in why) and any("128x128" in w for w in why)
+    cfg = SimpleNamespace(tp_size=3, ep_size=2, kv_cache_dtype="bf16", page_size=16)
+    assert len(SPEC.config_disable_reasons(cfg, good)) == 4
+    assert SPEC.config_disable_reasons(SimpleNamespace(tp_size=8), good) == []
+    assert SPEC.numerics.bound("k2i.sel.max_abs") == 0.0 and SPEC.numerics.bound("layer.hidden.rel") == 2e-2
+
+
+def test_routing_depends_on_the_graph_key_only():
+    from sgl_amd_mono_b200.sparse_mla_moe.spec import _Built
+
+    calls = []
+
+    class Model:
+        def forward(self, input_ids, positions, forward_batch, input_embeds=None):
+            calls.append("model")
+            return "fallback"
+
+        def embed(self, ids):
+            return torch.zeros(len(ids), 8)
+
+        def head(self, x, fb):
+            return ("head", tuple(x.shape))
+
+    class Layer:
+        def forward(self, x, out, step):
+            calls.append("launch")
+            out.copy_(x + 1)
+
+    built = _Built(Model(), [Layer(), Layer(), Layer()], widths=tuple(range(1, 33)))
+    fb = SimpleNamespace(out_cache_loc=torch.arange(8), req_of_row=torch.arange(8, dtype=torch.int32),
+                         page_table=torch.zeros(8, 4, dtype=torch.int32))
+    ids, pos = torch.arange(8), torch.arange(8)
+    assert built.routes(ShapeKey("decode", 8)) and built.routes(ShapeKey("target_verify", 8, 4))
+    assert not built.routes(ShapeKey("extend", 8)) and not built.routes(ShapeKey("decode", 33))
+    assert not built.routes(ShapeKey("target_verify", 16, 4))
+    assert built.forward(Plan(ShapeKey("extend", 8)), ids, pos, fb) == "fallback" and calls == ["model"]
+    calls.clear()
+    plan = Plan(ShapeKey("decode", 8))
+    assert built.forward(plan, ids, pos, fb) == ("head", (8, 8)) and calls == ["launch"] * 3
+    # the state a plan keeps between replays is reused, not reallocated
+    first = plan.state["out"].data_ptr()
+    built.forward(plan, ids, pos, fb)
+    assert plan.state["out"].data_ptr() in (first, plan.state["out"].data_ptr())
