@@ -3,10 +3,11 @@
     python bench.py --gpus N --steps K --warmup W            # this library, N GPUs (tensor parallel)
     python bench.py --impl reference --gpus N --steps K ...   # the CPU restatement on the host cores
 
-A step is one pass of one decoder layer's launch sequence over one batch of decode rows
-(default: the sparse-MLA FP8 MoE layer, 8 rows, tensor parallel over the N GPUs).  Layers
-with distinct weights are visited round-robin so every step streams its experts cold from
-HBM (one layer's picked experts are far larger than L2).  Rank 0 prints one JSON line.
+A step is one pass of one decoder layer's launch sequence (K1, K2i, K2) over one batch of decode rows:
+the sparse-MLA FP8 MoE layer, 8 rows, context lengths uniform in [4096, 65536], tensor parallel over the
+N GPUs (N = 1: the whole layer on one GPU).  Layers with distinct weights are visited round-robin so every
+step streams its experts cold from HBM (one layer's picked experts are far larger than L2).  Rank 0 prints
+one JSON line.  `--workload ffn` times the MoE FFN sub-block alone.
 """
 
 from __future__ import annotations
@@ -28,6 +29,8 @@ import torch  # noqa: E402
 
 METRIC = "us_per_decoder_layer"
 UNIT = "us"
+Q_LORA, KV_LORA, YA_COLS, IDX_ROWS = 1536, 512, 2304, 64 * 128
+NVLINK_GBS = 770.0  # measured peer copy per direction on this pool
 
 
 def peaks():
@@ -54,8 +57,9 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.index)],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            time.sleep(0.3)
         except Exception:
             self.proc = None
         return self
@@ -92,44 +96,109 @@ class ClockSampler:
 # --------------------------------------------------------------------------- workload
 def layer_cfg(rows: int, tp: int):
     """Per-rank dimensions of the sparse-MLA FP8 MoE decoder layer at tensor-parallel size tp."""
-    return dict(rows=rows, tp=tp, hidden=7168, experts=256, topk=8, inter=2048 // tp, has_shared=True, score_fn=1,
-                route_scale=2.5, eps=1e-6, swiglu_limit=0.0)
+    return dict(rows=rows, tp=tp, hidden=7168, heads=128, experts=256, topk=8, inter=2048 // tp, has_shared=True,
+                score_fn=1, route_scale=2.5, eps=1e-6, swiglu_limit=0.0, ctx_lo=4096, ctx_hi=65536)
 
 
-def make_layer_weights(cfg, seed: int, device):
-    """Random-init weights of one layer's MoE block in checkpoint layout, drawn on the device:
-    N(0, 0.02) quantised to e4m3 with 128x128 f32 block scales (block amax / 448)."""
+def _qblock(g, device, rows_, cols_, count=None, chunk=8, std=0.02):
+    """N(0, std) -> e4m3 + f32 128x128 block scales (block amax / 448), drawn on the device."""
+    n = count or 1
+    rp = -(-rows_ // 128) * 128
+    q = torch.empty(n, rows_, cols_, dtype=torch.float8_e4m3fn, device=device)
+    s = torch.empty(n, rp // 128, cols_ // 128, device=device)
+    for e0 in range(0, n, chunk):
+        e1 = min(n, e0 + chunk)
+        w = torch.zeros(e1 - e0, rp, cols_, device=device)
+        w[:, :rows_] = std * torch.randn(e1 - e0, rows_, cols_, generator=g, device=device)
+        blk = w.view(e1 - e0, rp // 128, 128, cols_ // 128, 128)
+        amax = blk.abs().amax(dim=(2, 4), keepdim=True)
+        sc = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+        q[e0:e1] = (blk / sc).clamp(-448, 448).to(torch.float8_e4m3fn).view(e1 - e0, rp, cols_)[:, :rows_]
+        s[e0:e1] = sc.view(e1 - e0, rp // 128, cols_ // 128)
+    return (q, s) if count else (q[0], s[0])
+
+
+def make_ffn_weights(cfg, seed: int, device, rank: int = 0):
+    """Router and norm are replicated (same draw on every rank); each rank holds its own slice of every expert."""
+    from sgl_amd_mono_b200.ffn import FfnWeights
+
     g = torch.Generator(device=device).manual_seed(1000 * seed + 7)
+    gr = torch.Generator(device=device).manual_seed(1000 * seed + 7 + 100 * (rank + 1))
     H, E, I = cfg["hidden"], cfg["experts"], cfg["inter"]
-    n = E + 1
-
-    def qblock(rows_, cols_, count, chunk=8):
-        q = torch.empty(count, rows_, cols_, dtype=torch.float8_e4m3fn, device=device)
-        s = torch.empty(count, -(-rows_ // 128), cols_ // 128, device=device)
-        for e0 in range(0, count, chunk):
-            e1 = min(count, e0 + chunk)
-            w = 0.02 * torch.randn(e1 - e0, rows_, cols_, generator=g, device=device)
-            blk = w.view(e1 - e0, rows_ // 128, 128, cols_ // 128, 128)
-            amax = blk.abs().amax(dim=(2, 4), keepdim=True)
-            sc = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
-            q[e0:e1] = (blk / sc).clamp(-448, 448).to(torch.float8_e4m3fn).view(e1 - e0, rows_, cols_)
-            s[e0:e1] = sc.view(e1 - e0, rows_ // 128, cols_ // 128)
-        return q, s
-
-    w13, w13_s = qblock(2 * I, H, n)
-    w2, w2_s = qblock(H, I, n)
-    return dict(
-        norm=(1 + 0.1 * torch.randn(H, generator=g, device=device)).to(torch.bfloat16),
-        gate_w=(0.02 * torch.randn(E, H, generator=g, device=device)).to(torch.bfloat16),
-        bias=(0.02 * torch.randn(E, generator=g, device=device)).float(),
-        w13=w13, w13_s=w13_s, w2=w2, w2_s=w2_s)
+    w13, w13_s = _qblock(gr, device, 2 * I, H, E + 1)
+    w2, w2_s = _qblock(gr, device, H, I, E + 1)
+    return FfnWeights(norm=(1 + 0.1 * torch.randn(H, generator=g, device=device)).to(torch.bfloat16),
+                      gate_w=(0.02 * torch.randn(E, H, generator=g, device=device)).to(torch.bfloat16),
+                      bias=(0.02 * torch.randn(E, generator=g, device=device)).float(), w13=w13, w13_s=w13_s, w2=w2, w2_s=w2_s)
 
 
-def expert_bytes(cfg):
-    H, I = cfg["hidden"], cfg["inter"]
-    up = 2 * I * H + (-(-2 * I // 128)) * (H // 128) * 4
-    down = H * I + (H // 128) * (I // 128) * 4
-    return up, down
+def make_layer_weights(cfg, seed: int, device, rank: int = 0):
+    """Random-init weights of one layer on one rank, checkpoint layout.  Replicated tensors (norms, q_a/kv_a, index
+    projections, router) are the same draw on every rank; head- and expert-sharded ones are drawn per rank."""
+    from sgl_amd_mono_b200.layer import LayerWeights
+
+    g = torch.Generator(device=device).manual_seed(1000 * seed + 11)
+    gr = torch.Generator(device=device).manual_seed(1000 * seed + 11 + 100 * (rank + 1))
+    H, hl = cfg["hidden"], cfg["heads"] // cfg["tp"]
+
+    def norm(n):
+        return (1 + 0.1 * torch.randn(n, generator=g, device=device)).to(torch.bfloat16)
+
+    wa, wa_s = _qblock(g, device, YA_COLS, H)
+    wiq, wiq_s = _qblock(g, device, IDX_ROWS, Q_LORA, std=0.05)
+    wqb, wqb_s = _qblock(gr, device, hl * 192, Q_LORA, std=0.05)
+    wuk, wuk_s = _qblock(gr, device, hl * KV_LORA, 128, std=0.08)
+    wuv, wuv_s = _qblock(gr, device, hl * 128, KV_LORA, std=0.05)
+    wo, wo_s = _qblock(gr, device, H, hl * 128)
+    return LayerWeights(attn_norm=norm(H), wa=wa, wa_s=wa_s, q_norm=norm(Q_LORA), kv_norm=norm(KV_LORA), wq_b=wqb, wq_b_s=wqb_s,
+                        w_uk=wuk, w_uk_s=wuk_s, wiq_b=wiq, wiq_b_s=wiq_s, w_uv=wuv, w_uv_s=wuv_s, w_o=wo, w_o_s=wo_s,
+                        ffn=make_ffn_weights(cfg, seed, device, rank))
+
+
+def make_caches_and_step(cfg, device, seed=0):
+    """Random FP8 latent / FP4 index caches for every earlier position of the requests, a permuted page table
+    (page 0 = pad page) and positions uniform in [ctx_lo, ctx_hi)."""
+    from sgl_amd_mono_b200.layer import Caches, Step
+
+    g = torch.Generator().manual_seed(9000 + seed)
+    rows = cfg["rows"]
+    pos = torch.randint(cfg["ctx_lo"], cfg["ctx_hi"], (rows,), generator=g).to(torch.int32)
+    max_pages = (cfg["ctx_hi"] + 63) // 64
+    n_pages = rows * max_pages + 1
+    table = (torch.randperm(n_pages - 1, generator=g)[: rows * max_pages] + 1).view(rows, max_pages).to(torch.int32)
+    gd = torch.Generator(device=device).manual_seed(77 + seed)
+    kv = torch.randint(0, 256, (n_pages * 64, 656), generator=gd, dtype=torch.uint8, device=device)
+    lat = kv[:, :512]
+    lat[(lat & 0x7F) == 0x7F] = 0x38
+    kv[:, 512:528] = (torch.rand(n_pages * 64, 4, generator=gd, device=device) * 0.02 + 0.002).view(torch.uint8).view(-1, 16)
+    kv[:, 528:] = torch.randn(n_pages * 64, 64, generator=gd, device=device).to(torch.bfloat16).view(torch.uint8).view(-1, 128)
+    idx = torch.randint(0, 256, (n_pages, 4352), generator=gd, dtype=torch.uint8, device=device)
+    idx[:, 4096:] = torch.randint(120, 128, (n_pages, 256), generator=gd, dtype=torch.uint8, device=device)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 64, 2, dtype=torch.float64) / 64))
+    ang = torch.arange(cfg["ctx_hi"] + 64, dtype=torch.float64)[:, None] * inv[None, :]
+    rope = torch.cat([ang.cos(), ang.sin()], 1).float().to(device)
+    req = torch.arange(rows, dtype=torch.int32)
+    slots = (table[req.long(), (pos // 64).long()].long() * 64 + (pos % 64).long()).to(torch.int32)
+    step = Step(positions=pos.to(device), slots=slots.to(device), req_of_row=req.to(device),
+                ctx_len=(pos + 1).to(torch.int32).to(device), page_table=table.to(device))
+    return Caches(kv=kv, idx=idx, rope_table=rope), step, pos
+
+
+def layer_bytes(cfg, distinct_experts: float, ctx_sum: int):
+    """Algorithmic HBM bytes of one layer step on one rank: every distinct weight byte once (FP8 = 1 B/elt + 4 B per
+    128x128 block), the KV records and index keys touched; activations and scratch excluded."""
+    H, hl, I, rows = cfg["hidden"], cfg["heads"] // cfg["tp"], cfg["inter"], cfg["rows"]
+
+    def fp8(n, k):
+        return n * k + (-(-n // 128)) * (k // 128) * 4
+
+    dense = (fp8(YA_COLS, H) + fp8(hl * 192, Q_LORA) + fp8(hl * 512, 128) + fp8(IDX_ROWS, Q_LORA) + fp8(hl * 128, 512) +
+             fp8(H, hl * 128) + cfg["experts"] * H * 2)
+    expert = fp8(2 * I, H) + fp8(H, I)
+    kv = rows * 2048 * 656
+    index = ctx_sum * 68
+    return dict(dense=dense, experts=distinct_experts * expert, kv=kv, index=index,
+                total=dense + distinct_experts * expert + kv + index, expert_each=expert, up_each=fp8(2 * I, H))
 
 
 def run_ours(args):
@@ -137,7 +206,7 @@ def run_ours(args):
 
     import sgl_amd_mono_b200  # noqa: F401
     from sgl_amd_mono_b200 import cabi
-    from sgl_amd_mono_b200.ffn import FfnBuild, FfnRunner, FfnWeights
+    from sgl_amd_mono_b200.layer import LayerBuild, LayerRunner
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -146,38 +215,54 @@ def run_ours(args):
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    cpu_group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        cpu_group = dist.new_group(backend="gloo")
     tp = args.shard_of or world
     cfg = layer_cfg(args.rows, tp)
     lib = cabi.lib()
+    rows, H = args.rows, cfg["hidden"]
 
-    layers = []
+    caches, step, pos = make_caches_and_step(cfg, dev)
+    build = LayerBuild(width=rows, tp=tp, max_ctx=cfg["ctx_hi"])
+    layers, reducer = [], None
     for li in range(args.layers):
-        w = make_layer_weights(cfg, seed=li, device=dev)
-        b = FfnBuild(width=args.rows, hidden=cfg["hidden"], inter=cfg["inter"], experts=cfg["experts"], topk=cfg["topk"],
-                     score_fn=cfg["score_fn"], has_shared=True, route_scale=cfg["route_scale"], eps=cfg["eps"])
-        layers.append(FfnRunner(b, FfnWeights(norm=w["norm"], gate_w=w["gate_w"], bias=w["bias"], w13=w["w13"],
-                                              w13_s=w["w13_s"], w2=w["w2"], w2_s=w["w2_s"]), dev))
+        w = make_layer_weights(cfg, seed=li, device=dev, rank=rank)
+        r = LayerRunner(build, w, caches, rank=rank, group=cpu_group, device=dev, reducer=reducer, world=world)
+        reducer = r.reducer
+        layers.append(r)
     g = torch.Generator(device=dev).manual_seed(5)
-    n_in = 16
-    xs = [torch.randn(args.rows, cfg["hidden"], generator=g, device=dev).to(torch.bfloat16) for _ in range(n_in)]
-    res = torch.randn(args.rows, cfg["hidden"], generator=g, device=dev).to(torch.bfloat16)
-    out = torch.empty_like(res)
+    n_in = 8
+    xs = [torch.randn(rows, H, generator=g, device=dev).to(torch.bfloat16) for _ in range(n_in)]
+    x_in = torch.empty_like(xs[0])  # static input of the captured end-to-end steps
+    out = torch.empty_like(xs[0])
 
-    # one CUDA graph per (layer, input): replay = one step, no host launch cost inside the timed region
+    def run_step(layer, x):
+        if args.workload == "ffn":
+            layer.ffn.ffn(x, out, None, True)
+        else:
+            layer.forward(x, out, step)
+
+    # one CUDA graph per (layer, input): a replay is one step with no host launch cost in the timed region
     stream = torch.cuda.Stream(dev)
-    graphs = []
+    graphs, e2e_graphs = [], []
     with torch.cuda.stream(stream):
         for li, r in enumerate(layers):
-            r.ffn(xs[li % n_in], out, res, True)  # warm caches / lazy init outside capture
+            run_step(r, xs[li % n_in])  # lazy initialisation outside capture
         stream.synchronize()
         for i in range(max(args.layers, n_in)):
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr, stream=stream):
-                layers[i % args.layers].ffn(xs[i % n_in], out, res, True)
+                run_step(layers[i % args.layers], xs[i % n_in])
             graphs.append(gr)
-    launches_per_step = 6
+        for li in range(args.layers):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                run_step(layers[li], x_in)
+            e2e_graphs.append(gr)
+    # kernels per step: K1 10, K2i 2, K2: attention 2, projections and quants 4, exchanges 2, MoE block 5
+    launches_per_step = 6 if args.workload == "ffn" else 25
 
     def barrier():
         if world > 1:
@@ -198,122 +283,162 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
-    step = lambda i: graphs[i % len(graphs)].replay()  # noqa: E731
-    timed(step, args.warmup)
+    step_fn = lambda i: graphs[i % len(graphs)].replay()  # noqa: E731
+    timed(step_fn, args.warmup)
     with ClockSampler(local) as cs:
-        ms = timed(step, args.steps)
+        ms = timed(step_fn, args.steps)
     clocks = cs.summary()
     us_per_step = ms * 1000.0 / args.steps
+    bad = [layers[0].reducer.status()] + [r.ffn.status() for r in layers] + [int(r.status[0].item()) for r in layers]
+    if any(bad):
+        raise SystemExit(f"a device wait gave up: status words {bad}")
 
-    # ---- end to end: host rows in, host rows out, every step, through the runner's public call
+    # ---- end to end: host rows in, host rows out, every step
     hx = [x.cpu().pin_memory() for x in xs]
-    hres = res.cpu().pin_memory()
-    hout = torch.empty_like(hres).pin_memory()
-    dx, dres = torch.empty_like(res), torch.empty_like(res)
+    hout = torch.empty_like(hx[0]).pin_memory()
 
     def e2e_step(i):
-        dx.copy_(hx[i % n_in], non_blocking=True)
-        dres.copy_(hres, non_blocking=True)
-        layers[i % args.layers].ffn(dx, out, dres, True, stream=stream)
+        x_in.copy_(hx[i % n_in], non_blocking=True)
+        e2e_graphs[i % args.layers].replay()
         hout.copy_(out, non_blocking=True)
         stream.synchronize()
 
     timed(e2e_step, args.warmup)
     e2e_us = timed(e2e_step, args.steps) * 1000.0 / args.steps
-    row_bytes = args.rows * cfg["hidden"] * 2
+    row_bytes = rows * H * 2
 
-    # ---- every kernel of the step timed alone over the same steps (separate C-ABI calls, CUDA events
-    # around each on its stream, L2 flushed before each step)
-    up_b, down_b = expert_bytes(cfg)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    names = ["norm_quant", "router", "moe_up", "quant128", "moe_down"]
-    per_stage = {n: [] for n in names}
-    unions, evs = [], []
-    with torch.cuda.stream(stream):
-        for i in range(args.steps):
-            r = layers[i % args.layers]
-            calls = r.stage_calls(xs[i % n_in], out, res, True)
-            flush.zero_()
-            marks = [torch.cuda.Event(enable_timing=True) for _ in range(len(calls) + 1)]
-            marks[0].record(stream)
-            for j, (name, a) in enumerate(calls):
-                lib.call(name, a, stream.cuda_stream)
-                marks[j + 1].record(stream)
-            evs.append(marks)
-            L = r.step_layout
-            unions.append(r.scratch[L.union_count:L.union_count + 4].view(torch.int32).clone())
-        stream.synchronize()
-    for marks in evs:
-        for j, n in enumerate(names):
-            per_stage[n].append(marks[j].elapsed_time(marks[j + 1]) * 1000.0)
-    stage_us = {n: round(statistics.mean(v), 2) for n, v in per_stage.items()}
-    up_us = per_stage["moe_up"]
-    u_mean = float(sum(int(u.item()) for u in unions)) / len(unions)
-    up_bytes = u_mean * up_b
+    # ---- the dominant kernel (expert gate/up GEMV + SwiGLU) timed alone: L2 flushed, CUDA events on its stream.
+    # Single-GPU runs only: with peers, an extra launch on one rank would have to be mirrored on all.
     peak, peak_kind = peaks()
-    up_gbs = up_bytes / (statistics.mean(up_us) * 1e-6) / 1e9
-    layer_bytes = u_mean * (up_b + down_b) + cfg["experts"] * cfg["hidden"] * 2
+    u_mean, up_us = float("nan"), float("nan")
+    by = layer_bytes(cfg, 0.0, int((pos + 1).sum()))
+    if world == 1:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        ups, unions = [], []
+        with torch.cuda.stream(stream):
+            for i in range(min(args.steps, 50)):
+                r = layers[i % args.layers]
+                run_step(r, xs[i % n_in])  # leaves this step's routing and quantised rows in the block's scratch
+                f = r.ffn
+                f_in = r.a[:rows] if args.workload != "ffn" else xs[i % n_in]
+                calls = dict(f.stage_calls(f_in, out, None, False))
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                lib.call("moe_up", calls["moe_up"], stream.cuda_stream)
+                e1.record(stream)
+                ups.append((e0, e1))
+                L = f.step_layout
+                unions.append(f.scratch[L.union_count:L.union_count + 4].view(torch.int32).clone())
+            stream.synchronize()
+        up_us = statistics.mean(a.elapsed_time(b) * 1000.0 for a, b in ups)
+        u_mean = float(sum(int(u.item()) for u in unions)) / len(unions)
+    else:
+        L = layers[0].ffn.step_layout
+        u_mean = float(layers[0].ffn.scratch[L.union_count:L.union_count + 4].view(torch.int32).item())
+    by = layer_bytes(cfg, u_mean, int((pos + 1).sum()))
+    up_bytes = u_mean * by["up_each"]
+    up_gbs = up_bytes / (up_us * 1e-6) / 1e9 if up_us == up_us else None
+    if args.workload == "ffn":
+        step_bytes, nvl = u_mean * by["expert_each"] + cfg["experts"] * H * 2, 0.0
+    else:
+        step_bytes = by["total"]
+        nvl = 2 * rows * H * 4 * (world - 1)  # two exchanges; tagged words are twice the bf16 payload
+    t_roof_us = (step_bytes / (peak * 1e9) + nvl / (NVLINK_GBS * 1e9)) * 1e6
 
+    what = ("MoE FFN sub-block only" if args.workload == "ffn" else
+            "whole layer: K1 (norms, q_a/kv_a, KV + index records, q_b, W_UK, index query), K2i (index scores, exact top-2048), "
+            "K2 (sparse MLA, W_UV, o_proj, all-reduce + residual, router top-8 of 256, routed + shared experts, all-reduce + residual)")
     result = {
         "metric": METRIC, "value": round(us_per_step, 3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(us_per_step / 1000.0, 6), "higher_is_better": False,
-        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (f32 accumulate, bf16 rows)", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp8_e4m3 weights and KV, fp4_e2m1 index, f32 accumulate, bf16 rows", "data": "synthetic",
         "config": {
-            "workload": f"sparse-MLA FP8 MoE decoder layer, {args.rows} decode rows, TP{tp}: MoE FFN sub-block "
-                        "(RMSNorm+quant, router top-8 of 256, routed+shared experts); attention stages not in this line",
-            "rows": args.rows, "tp": tp, "layers_rotated": args.layers, "hidden": cfg["hidden"], "experts": 256, "topk": 8,
-            "inter_per_rank": cfg["inter"], "l2": "every step streams >1 GB of distinct expert weights (inputs larger than L2)",
-            "launch": "CUDA graph replay per step", "distinct_experts_per_step": u_mean,
+            "workload": f"sparse-MLA FP8 MoE decoder layer, {rows} decode rows, TP{tp}" +
+                        (f" (rank 0's shard alone on {world} GPU)" if args.shard_of else "") + f"; {what}",
+            "rows": rows, "tp": tp, "layers_rotated": args.layers, "hidden": H, "heads_per_rank": cfg["heads"] // tp,
+            "experts": 256, "topk": 8, "inter_per_rank": cfg["inter"],
+            "context": "uniform in [4096, 65536), 64-token pages, FP8 latent records of 656 B, FP4 index keys of 68 B, exact top-2048",
+            "l2": "every step streams far more distinct expert weights than L2 holds (inputs larger than L2)",
+            "launch": "CUDA graph replay per step", "distinct_experts_per_step": round(u_mean, 2),
         },
-        "e2e": {"value": round(e2e_us, 3), "unit": UNIT, "h2d_bytes_per_step": 2 * row_bytes, "d2h_bytes_per_step": row_bytes},
+        "e2e": {"value": round(e2e_us, 3), "unit": UNIT, "h2d_bytes_per_step": row_bytes, "d2h_bytes_per_step": row_bytes},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
         "roofline": {
-            "bound": "hbm", "kernel": "stream_kernel<NT,SWIGLU> (expert gate/up GEMV + SwiGLU, TMA ring)", "achieved": round(up_gbs, 1),
-            "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(up_gbs / peak, 4), "traffic": None,
-            "bytes_per_launch": up_bytes, "us_per_launch": round(statistics.mean(up_us), 3),
-            "timed": "second pass over the same steps, CUDA events around the kernel on its stream, L2 flushed before each",
-            "stages_us": stage_us, "down_gbs": round(u_mean * down_b / (stage_us["moe_down"] * 1e-6) / 1e9, 1),
-            "step_bytes": layer_bytes, "step_frac_of_hbm_roofline": round(layer_bytes / (us_per_step * 1e-6) / 1e9 / peak, 4),
+            "bound": "hbm", "kernel": "stream_kernel<NT,SWIGLU> (expert gate/up GEMV + SwiGLU, TMA ring)",
+            "achieved": round(up_gbs, 1) if up_gbs else None, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+            "frac": round(up_gbs / peak, 4) if up_gbs else None, "traffic": None, "bytes_per_launch": round(up_bytes),
+            "us_per_launch": round(up_us, 3) if up_gbs else None,
+            "timed": "the kernel alone after each of the first steps, CUDA events on its stream, L2 flushed before each (1-GPU runs)",
+            "step_bytes_hbm": round(step_bytes), "step_bytes_nvlink_out": round(nvl), "step_roofline_us": round(t_roof_us, 2),
+            "step_frac_of_roofline": round(t_roof_us / us_per_step, 4),
+            "step_bytes": {k: round(v) for k, v in by.items() if k in ("dense", "experts", "kv", "index")},
         },
     }
     if rank == 0 and world == 1 and not args.no_cpu:
-        result["cpu_baseline"] = cpu_baseline(cfg, seconds=args.cpu_seconds)
+        result["cpu_baseline"] = cpu_baseline(cfg, args.workload, seconds=args.cpu_seconds)
     if rank == 0:
         print(json.dumps(result))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
 # --------------------------------------------------------------------------- CPU arm
-class CpuBlock:
-    """The oracle's MoE block on the host cores.  Weights of `experts_sample` experts are drawn
-    once; a step times norm + router whole and the sampled experts, and scales the expert time
-    to the number of distinct experts the step's routing picked (+ the shared expert)."""
+class CpuLayer:
+    """The oracle's layer on the host cores, on a bounded sample.  Weights of the attention side and of
+    `experts_sample` experts are drawn once (rank 0's shard); a step times K1, the router and the attention-output
+    projections whole, the index scores + top-k and the sparse attention of ONE row (scaled to the step's rows) at a
+    context of `ctx` keys, and the sampled experts (scaled to the step's distinct experts)."""
 
-    def __init__(self, cfg, experts_sample: int):
+    def __init__(self, cfg, workload: str, experts_sample: int, ctx: int = 34816):
+        from oracle import layer as L
         from oracle import quant as Q
 
-        self.cfg, self.n = cfg, experts_sample
+        self.cfg, self.n, self.workload, self.ctx = cfg, experts_sample, workload, ctx
         g = torch.Generator().manual_seed(1)
-        H, I, E = cfg["hidden"], cfg["inter"], cfg["experts"]
-        self.xs = [torch.randn(cfg["rows"], H, generator=g).to(torch.bfloat16) for _ in range(4)]
+        H, I, E, rows = cfg["hidden"], cfg["inter"], cfg["experts"], cfg["rows"]
+        self.ocfg = L.layer_cfg(tp=cfg["tp"], max_ctx=ctx + 64)
+        self.xs = [torch.randn(rows, H, generator=g).to(torch.bfloat16) for _ in range(2)]
         self.norm = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
         self.gate = (0.02 * torch.randn(E, H, generator=g)).to(torch.bfloat16)
         self.bias = (0.02 * torch.randn(E, generator=g)).numpy()
         self.w13, self.w13_s = Q.quant_weight_block128(0.02 * torch.randn(experts_sample, 2 * I, H, generator=g))
         self.w2, self.w2_s = Q.quant_weight_block128(0.02 * torch.randn(experts_sample, H, I, generator=g))
+        if workload != "ffn":
+            ecfg = dict(self.ocfg, experts=1)  # attention-side weights only (the experts are sampled above)
+            self.w = L.make_weights(ecfg, rank=0, seed=3)
+            self.caches, self.step = L.make_step(self.ocfg, 1, ctx, ctx + 1, seed=1)
+            self.step_rows = {k: (v.repeat(rows) if v.dim() == 1 else v) for k, v in self.step.items()}
+        self.distinct = 0
 
-    def step(self, i: int) -> float:
+    def step_us(self, i: int) -> float:
+        from oracle import layer as L
         from oracle import moe as M
         from oracle import quant as Q
 
-        cfg = self.cfg
+        cfg, rows = self.cfg, self.cfg["rows"]
+        total = 0.0
+        x = self.xs[i % 2]
+        if self.workload != "ffn":
+            t0 = time.perf_counter()
+            f = L.k1(x, self.w, self.caches, self.step_rows, self.ocfg)
+            total += time.perf_counter() - t0
+            t0 = time.perf_counter()
+            one = {k: (v[:1] if v.dim() == 1 else v) for k, v in self.step.items()}
+            sel = L.k2i(f["q_rec"][:1], f["iw"][:1], self.caches, one)
+            o1 = L.attention(f["q_lat"][:1], f["q_rope"][:1], [sel[0][1]], self.caches, one, self.ocfg)
+            total += (time.perf_counter() - t0) * rows
+            t0 = time.perf_counter()
+            L.attn_out_partial(o1.repeat(rows, 1), self.w, self.ocfg)
+            total += time.perf_counter() - t0
         t0 = time.perf_counter()
-        _, xn, xq, xs = M.rmsnorm_quant(self.xs[i % 4], self.norm, cfg["eps"])
+        _, xn, xq, xs = M.rmsnorm_quant(x, self.norm, cfg["eps"])
         logits = M.router_logits(xn, self.gate)
         ids, _ = M.route(logits, self.bias, cfg["topk"], M.SCORE_SIGMOID_BIAS, cfg["route_scale"])
-        t_route = time.perf_counter() - t0
+        total += time.perf_counter() - t0
         t0 = time.perf_counter()
         for e in range(self.n):
             mid = M.expert_mid(xq, xs, self.w13[e], self.w13_s[e], 0.0)
@@ -321,19 +446,23 @@ class CpuBlock:
             Q.gemv_fp8(mq, ms, self.w2[e], self.w2_s[e])
         t_exp = (time.perf_counter() - t0) / self.n
         self.distinct = len(set(ids.reshape(-1).tolist())) + 1
-        return (t_route + self.distinct * t_exp) * 1e6
+        return (total + self.distinct * t_exp) * 1e6
 
     def describe(self, steps: int) -> str:
-        return (f"{steps} steps; per step norm+router timed whole, {self.n} expert(s) timed and scaled to the "
-                f"step's distinct experts ({self.distinct})")
+        s = (f"{steps} steps; norm + router timed whole, {self.n} expert(s) timed and scaled to the step's distinct "
+             f"experts ({self.distinct})")
+        if self.workload != "ffn":
+            s += (f"; K1 and the attention-output projections timed whole; index scores + top-2048 + sparse attention timed for "
+                  f"one row at {self.ctx} keys (the mean context) and scaled to {self.cfg['rows']} rows")
+        return s
 
 
-def cpu_baseline(cfg, seconds: float = 15.0):
-    blk = CpuBlock(cfg, experts_sample=2)
-    blk.step(0)
+def cpu_baseline(cfg, workload, seconds: float = 15.0):
+    blk = CpuLayer(cfg, workload, experts_sample=2)
+    blk.step_us(0)
     vals, t0 = [], time.perf_counter()
     while not vals or (time.perf_counter() - t0 < seconds and len(vals) < 50):
-        vals.append(blk.step(len(vals)))
+        vals.append(blk.step_us(len(vals)))
     return {"value": round(statistics.median(vals), 1), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
             "sample": blk.describe(len(vals))}
 
@@ -344,16 +473,16 @@ def run_reference(args):
         return
     tp = args.shard_of or args.gpus
     cfg = layer_cfg(args.rows, tp)
-    blk = CpuBlock(cfg, experts_sample=1)
+    blk = CpuLayer(cfg, args.workload, experts_sample=1)
     budget, t0, vals = 150.0, time.perf_counter(), []
     for i in range(args.warmup + args.steps):
         if vals and time.perf_counter() - t0 > budget:
             break  # bounded: the remaining steps would repeat the same sample
-        v = blk.step(i)
+        v = blk.step_us(i)
         if i >= args.warmup or args.warmup + args.steps <= 3:
             vals.append(v)
     if not vals:
-        vals.append(blk.step(0))
+        vals.append(blk.step_us(0))
     v = statistics.mean(vals)
     base = {"value": round(v, 1), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
             "sample": blk.describe(len(vals)) + (f"; stopped after {len(vals)} of {args.steps} timed steps (time bound)"
@@ -361,10 +490,11 @@ def run_reference(args):
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(v, 1), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(v / 1000.0, 3), "higher_is_better": False, "scaling": "strong",
-        "vs_baseline": None, "dtype": "fp8_e4m3 (dequantised, f64 accumulate)", "data": "synthetic",
-        "config": {"workload": f"sparse-MLA FP8 MoE decoder layer, {args.rows} decode rows, TP{tp}: MoE FFN sub-block, "
-                               "CPU restatement of the reference's torch goldens (the reference's own kernels are "
-                               "FlyDSL/ROCm-only and cannot run on this box)", "rows": args.rows, "tp": tp},
+        "vs_baseline": None, "dtype": "fp8_e4m3 / fp4_e2m1 dequantised, f64 accumulate", "data": "synthetic",
+        "config": {"workload": f"sparse-MLA FP8 MoE decoder layer, {args.rows} decode rows, TP{tp}, rank 0's share: CPU "
+                               "restatement of the reference's torch goldens (the reference's own kernels are FlyDSL/ROCm-only "
+                               "and cannot run on this box)" + (" [MoE FFN sub-block only]" if args.workload == "ffn" else ""),
+                   "rows": args.rows, "tp": tp},
         "cpu_baseline": base,
         "e2e": {"value": round(v, 1), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -378,6 +508,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--layers", type=int, default=2, help="distinct-weight layers visited round-robin")
+    ap.add_argument("--workload", default="layer", choices=["layer", "ffn"])
     ap.add_argument("--shard-of", type=int, default=0, help="run rank 0's shard of a TP-<n> layer on one GPU (profiling)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)

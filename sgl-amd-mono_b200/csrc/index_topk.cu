@@ -26,7 +26,7 @@ __device__ __forceinline__ float e8m0_to_f32(uint32_t code) {
   return code == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(code << 23);  // 2^-127 is subnormal
 }
 
-constexpr int kPagesPerWarp = 4;
+constexpr int kPagesPerWarp = 2;
 constexpr int kScoreWarps = 4;
 
 // CTA = 4 warps; blockIdx.y = row, blockIdx.x = group of 16 pages (1024 keys); warp w takes pages 4w..4w+3.
@@ -126,11 +126,36 @@ cudaError_t launch_index_score(const B200IndexScoreArgs& a, cudaStream_t s) {
 }
 
 // ------------------------------------------------------------------ exact top-k
-// One CTA of 1024 threads per row.
+// One CTA of 1024 threads per row; the row's scores (L2-resident, written by the launch before) are
+// read in batches of eight independent loads per thread so that their latency overlaps.
+constexpr int kTopkBatch = 8;
+
+template <typename F>
+__device__ __forceinline__ void for_keys(const float* sc, int n, int tid, F&& f) {
+  for (int i0 = 0; i0 < n; i0 += 1024 * kTopkBatch) {
+    unsigned key[kTopkBatch];
+#pragma unroll
+    for (int j = 0; j < kTopkBatch; ++j) {
+      const int i = i0 + j * 1024 + tid;
+      key[j] = i < n ? radix_key(__ldcg(sc + i)) : 0u;
+    }
+#pragma unroll
+    for (int j = 0; j < kTopkBatch; ++j) {
+      const int i = i0 + j * 1024 + tid;
+      if (i0 + j * 1024 < n) f(key[j], i < n, i, (i0 >> 10) + j);  // warp-uniform condition
+    }
+  }
+}
+
 __global__ __launch_bounds__(1024) void topk_kernel(B200TopkArgs a) {
   __shared__ unsigned int hist[256];
-  __shared__ unsigned int whist[32][256];  // per-warp histograms: score exponents cluster in a few digits
-  __shared__ unsigned int s_prefix, s_need, s_scan[32], s_base_gt, s_base_eq;
+  // per-warp histograms (score exponents cluster in a few digits); after the select the same storage
+  // holds, per (1024-key chunk, warp), the taken counts and then their prefixes
+  __shared__ __align__(8) unsigned int s_raw[32 * 256];
+  unsigned int (*whist)[256] = reinterpret_cast<unsigned int (*)[256]>(s_raw);
+  unsigned long long* s_cnt = reinterpret_cast<unsigned long long*>(s_raw);
+  __shared__ unsigned int s_prefix, s_need;
+  __shared__ unsigned long long s_warp_tot[32];
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n = a.ctx_len[t];
   const float* sc = a.scores + (size_t)t * a.score_stride;
@@ -152,18 +177,14 @@ __global__ __launch_bounds__(1024) void topk_kernel(B200TopkArgs a) {
     __syncthreads();
     const unsigned prefix = s_prefix;
     const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-    for (int i0 = 0; i0 < n; i0 += 1024) {
-      const int i = i0 + tid;
+    for_keys(sc, n, tid, [&](unsigned key, bool valid, int, int) {
       unsigned digit = 256u;  // not a candidate
-      if (i < n) {
-        const unsigned key = radix_key(sc[i]);
-        if ((key & mask) == prefix) digit = (key >> shift) & 0xffu;
-      }
+      if (valid && (key & mask) == prefix) digit = (key >> shift) & 0xffu;
       // lanes with the same digit elect one to add their count
       const unsigned peers = __match_any_sync(0xffffffffu, digit);
       if (digit < 256u && lane == __ffs(peers) - 1) whist[warp][digit] += (unsigned)__popc(peers);
       __syncwarp();
-    }
+    });
     __syncthreads();
     if (tid < 256) {
       unsigned c = 0;
@@ -201,49 +222,233 @@ __global__ __launch_bounds__(1024) void topk_kernel(B200TopkArgs a) {
     __syncthreads();
   }
   const unsigned thr = s_prefix, need_eq = s_need;
-  if (tid == 0) {
-    s_base_gt = 0;
-    s_base_eq = 0;
+  const int nchunk = (n + 1023) >> 10;
+  if (nchunk > 64) {  // cannot happen for contexts up to 65536 keys; refuse rather than overrun
+    if (tid == 0) a.topk_count[t] = -1;
+    return;
+  }
+  // emit in ascending position: everything above the threshold and the first need_eq keys equal to it.
+  // 1) per (chunk, warp) counts of keys above / equal (low / high word)
+  for_keys(sc, n, tid, [&](unsigned key, bool valid, int, int chunk) {
+    const unsigned bg = __ballot_sync(0xffffffffu, valid && key > thr), be = __ballot_sync(0xffffffffu, valid && key == thr);
+    if (lane == 0) s_cnt[chunk * 32 + warp] = (unsigned long long)__popc(bg) | ((unsigned long long)__popc(be) << 32);
+  });
+  __syncthreads();
+  // 2) exclusive scan over (chunk, warp) in position order: two entries per thread
+  {
+    const int total = nchunk * 32;
+    const unsigned long long a0 = 2 * tid < total ? s_cnt[2 * tid] : 0ull, a1 = 2 * tid + 1 < total ? s_cnt[2 * tid + 1] : 0ull;
+    const unsigned long long local = a0 + a1;
+    unsigned long long incl = local;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned long long o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    if (lane == 31) s_warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      unsigned long long v = s_warp_tot[lane], sc2 = v;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const unsigned long long o = __shfl_up_sync(0xffffffffu, sc2, off);
+        if (lane >= off) sc2 += o;
+      }
+      s_warp_tot[lane] = sc2 - v;  // exclusive
+    }
+    __syncthreads();
+    const unsigned long long excl = s_warp_tot[warp] + incl - local;
+    if (2 * tid < total) s_cnt[2 * tid] = excl;
+    if (2 * tid + 1 < total) s_cnt[2 * tid + 1] = excl + a0;
   }
   __syncthreads();
-  // emit in ascending position: everything above the threshold, and the first need_eq keys equal to it
-  for (int i0 = 0; i0 < n; i0 += 1024) {
-    const int i = i0 + tid;
-    unsigned key = 0;
-    if (i < n) key = radix_key(sc[i]);
-    const bool gt = i < n && key > thr, eq = i < n && key == thr;
+  // 3) write
+  for_keys(sc, n, tid, [&](unsigned key, bool valid, int i, int chunk) {
+    const bool gt = valid && key > thr, eq = valid && key == thr;
     const unsigned bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
-    if (lane == 0) s_scan[warp] = (unsigned)__popc(bg) | ((unsigned)__popc(be) << 16);
-    __syncthreads();
-    unsigned before_gt = 0, before_eq = 0, tot_gt = 0, tot_eq = 0;
-    for (int w = 0; w < 32; ++w) {
-      const unsigned v = s_scan[w];
-      if (w < warp) {
-        before_gt += v & 0xffffu;
-        before_eq += v >> 16;
-      }
-      tot_gt += v & 0xffffu;
-      tot_eq += v >> 16;
-    }
+    const unsigned long long pre = s_cnt[chunk * 32 + warp];
     const unsigned lm = (1u << lane) - 1u;
-    const unsigned my_gt = s_base_gt + before_gt + __popc(bg & lm);
-    const unsigned my_eq = s_base_eq + before_eq + __popc(be & lm);
-    // position in the output = (taken above-threshold keys before me) + (taken equal keys before me)
+    const unsigned my_gt = (unsigned)(pre & 0xffffffffu) + __popc(bg & lm);
+    const unsigned my_eq = (unsigned)(pre >> 32) + __popc(be & lm);
+    // position in the output = (keys above the threshold before me) + (taken equal keys before me)
     const unsigned eq_taken_before = my_eq < need_eq ? my_eq : need_eq;
     if (gt) out[my_gt + eq_taken_before] = i;
     if (eq && my_eq < need_eq) out[my_gt + my_eq] = i;
-    __syncthreads();
-    if (tid == 0) {
-      s_base_gt += tot_gt;
-      s_base_eq += tot_eq;
-    }
-    __syncthreads();
-  }
+  });
   if (tid == 0) a.topk_count[t] = a.k;
 }
 
+// ------------------------------------------------------------------ exact top-k, one cluster per row
+// Eight CTAs (a thread-block cluster) share a row of up to 65536 scores: CTA r owns positions
+// [8192 r, 8192 r + 8192) and keeps its keys in registers (8 per thread), so the scores are read once.
+// Per radix pass every CTA builds its local 256-bin histogram, the cluster meets at a hardware barrier,
+// and every CTA sums the eight histograms through distributed shared memory and takes the same digit
+// decision; the write phase orders the CTAs' outputs by their totals, exchanged the same way.
+constexpr int kTopkCluster = 8, kTopkPer = 8;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// read a 32-bit word of CTA `rank`'s shared memory at the address `local` has in this CTA
+__device__ __forceinline__ uint32_t dsmem_ld_u32(const void* local, uint32_t rank) {
+  uint32_t addr = (uint32_t)__cvta_generic_to_shared(local), remote, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+__global__ __cluster_dims__(kTopkCluster, 1, 1) __launch_bounds__(1024) void topk_cluster_kernel(B200TopkArgs a) {
+  __shared__ unsigned int whist[32][256];
+  __shared__ unsigned int hist[2][256];      // local histogram, double-buffered across passes
+  __shared__ unsigned int s_tot[2];          // this CTA's (above, equal) totals
+  __shared__ unsigned int s_cnt[kTopkPer * 32][2], s_pre[kTopkPer * 32][2];
+  const int t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t rank = cluster_ctarank();
+  const int n = a.ctx_len[t];
+  const float* sc = a.scores + (size_t)t * a.score_stride;
+  int* out = a.topk_idx + (size_t)t * a.k;
+  if (n <= a.k) {  // the whole cluster takes this branch
+    for (int i = rank * 1024 + tid; i < n; i += kTopkCluster * 1024) out[i] = i;
+    if (rank == 0 && tid == 0) a.topk_count[t] = n;
+    return;
+  }
+  const int base = (int)rank * kTopkPer * 1024;
+  unsigned key[kTopkPer];
+#pragma unroll
+  for (int j = 0; j < kTopkPer; ++j) {
+    const int i = base + j * 1024 + tid;
+    key[j] = i < n ? radix_key(__ldcg(sc + i)) : 0u;
+  }
+  unsigned prefix = 0, need = (unsigned)a.k;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+    for (int i = tid; i < 32 * 256; i += 1024) (&whist[0][0])[i] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kTopkPer; ++j) {
+      const int i = base + j * 1024 + tid;
+      unsigned digit = 256u;
+      if (i < n && (key[j] & mask) == prefix) digit = (key[j] >> shift) & 0xffu;
+      const unsigned peers = __match_any_sync(0xffffffffu, digit);
+      if (digit < 256u && lane == __ffs(peers) - 1) whist[warp][digit] += (unsigned)__popc(peers);
+      __syncwarp();
+    }
+    __syncthreads();
+    unsigned int* hl = hist[pass & 1];
+    if (tid < 256) {
+      unsigned c = 0;
+      for (int w = 0; w < 32; ++w) c += whist[w][tid];
+      hl[tid] = c;
+    }
+    cluster_sync_all();  // every CTA's local histogram of this pass is complete (and visible)
+    // the cluster-wide histogram, summed by every CTA for itself; the buffer of this pass is not
+    // written again before the barrier of the pass after next, so no second barrier is needed
+    __shared__ unsigned int ghist[256];
+    if (tid < 256) {
+      unsigned c = 0;
+      for (uint32_t r = 0; r < kTopkCluster; ++r) c += dsmem_ld_u32(&hl[tid], r);
+      ghist[tid] = c;
+    }
+    __syncthreads();
+    __shared__ unsigned int s_found[2];
+    if (warp == 0) {
+      unsigned run = 0;
+      int found = -1;
+      for (int b0 = 224; b0 >= 0 && found < 0; b0 -= 32) {
+        const unsigned cnt = ghist[b0 + 31 - lane];
+        unsigned incl = cnt;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const unsigned o = __shfl_up_sync(0xffffffffu, incl, off);
+          if (lane >= off) incl += o;
+        }
+        const unsigned ballot = __ballot_sync(0xffffffffu, run + incl >= need);
+        if (ballot) {
+          const int l = __ffs(ballot) - 1;
+          const unsigned before = run + __shfl_sync(0xffffffffu, incl, l) - __shfl_sync(0xffffffffu, cnt, l);
+          found = b0 + 31 - l;
+          if (lane == 0) {
+            s_found[0] = (unsigned)found;
+            s_found[1] = need - before;
+          }
+        } else {
+          run += __shfl_sync(0xffffffffu, incl, 31);
+        }
+      }
+    }
+    __syncthreads();
+    prefix |= s_found[0] << shift;
+    need = s_found[1];
+    __syncthreads();
+  }
+  const unsigned thr = prefix, need_eq = need;
+  // per (chunk, warp) counts of this CTA's keys above / equal to the threshold
+#pragma unroll
+  for (int j = 0; j < kTopkPer; ++j) {
+    const int i = base + j * 1024 + tid;
+    const unsigned bg = __ballot_sync(0xffffffffu, i < n && key[j] > thr), be = __ballot_sync(0xffffffffu, i < n && key[j] == thr);
+    if (lane == 0) {
+      s_cnt[j * 32 + warp][0] = (unsigned)__popc(bg);
+      s_cnt[j * 32 + warp][1] = (unsigned)__popc(be);
+    }
+  }
+  __syncthreads();
+  if (warp < 2) {  // warp 0 scans the "above" counts, warp 1 the "equal" counts: 256 entries, 8 per lane
+    unsigned v[kTopkPer], sum = 0;
+#pragma unroll
+    for (int q = 0; q < kTopkPer; ++q) {
+      v[q] = s_cnt[lane * kTopkPer + q][warp];
+      sum += v[q];
+    }
+    unsigned incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    unsigned run = incl - sum;
+#pragma unroll
+    for (int q = 0; q < kTopkPer; ++q) {
+      s_pre[lane * kTopkPer + q][warp] = run;
+      run += v[q];
+    }
+    if (lane == 31) s_tot[warp] = incl;
+  }
+  cluster_sync_all();  // totals of every CTA are in place
+  unsigned before_gt = 0, before_eq = 0;
+  for (uint32_t r = 0; r < rank; ++r) {
+    before_gt += dsmem_ld_u32(&s_tot[0], r);
+    before_eq += dsmem_ld_u32(&s_tot[1], r);
+  }
+#pragma unroll
+  for (int j = 0; j < kTopkPer; ++j) {
+    const int i = base + j * 1024 + tid;
+    const bool gt = i < n && key[j] > thr, eq = i < n && key[j] == thr;
+    const unsigned bg = __ballot_sync(0xffffffffu, gt), be = __ballot_sync(0xffffffffu, eq);
+    const unsigned lm = (1u << lane) - 1u;
+    const unsigned my_gt = before_gt + s_pre[j * 32 + warp][0] + __popc(bg & lm);
+    const unsigned my_eq = before_eq + s_pre[j * 32 + warp][1] + __popc(be & lm);
+    const unsigned eq_taken_before = my_eq < need_eq ? my_eq : need_eq;
+    if (gt) out[my_gt + eq_taken_before] = i;
+    if (eq && my_eq < need_eq) out[my_gt + my_eq] = i;
+  }
+  if (rank == 0 && tid == 0) a.topk_count[t] = a.k;
+  cluster_sync_all();  // no CTA may exit while a peer still reads its shared memory
+}
+
 cudaError_t launch_topk(const B200TopkArgs& a, cudaStream_t s) {
-  topk_kernel<<<a.rows, 1024, 0, s>>>(a);
+  if (a.score_stride <= kTopkCluster * kTopkPer * 1024) {  // a row fits one cluster's registers
+    dim3 grid(kTopkCluster, a.rows);
+    topk_cluster_kernel<<<grid, 1024, 0, s>>>(a);
+  } else {
+    topk_kernel<<<a.rows, 1024, 0, s>>>(a);
+  }
   return cudaGetLastError();
 }
 

@@ -90,3 +90,18 @@ def test_layer_shard_against_oracle(lib, rows, tokens_per_request, ctx):
     assert e < 2e-2, e
     # rows are independent of each other: a verify row sees its earlier siblings through the cache only
     assert not torch.isnan(out.float()).any()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_layer_two_ranks_over_cuda_ipc():
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29651", os.path.join(root, "tests", "mgpu_layer.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "layer ok" in r.stdout
