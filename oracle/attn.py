@@ -87,8 +87,8 @@ def index_scores(q_rec: torch.Tensor, w: torch.Tensor, k_rec: torch.Tensor) -> n
     for one row: q_rec u8 [heads, 68], w f32 [heads], k_rec u8 [ctx, 68]
     (test/kernels/test_deepseek_v41_k2i.py:149-167 `ref_logits`).
     Order: the 32-dim group sums are exact (multiples of 1/4 below 2^11); groups are added g = 0..3 after
-    scaling; heads are added in the kernel's order: for each 16-head tile, lanes hold heads (i, i+8), the pair
-    is added first, then an xor tree over i (4, 2, 1), then tiles 0..3 in order."""
+    scaling; heads are added in the kernel's order: lane i holds heads (i, i+8) of every 16-head tile; the pair
+    is added first, the four tiles' pairs are added in tile order, then an xor tree over i (4, 2, 1)."""
     qv = Q.dequantize_mxfp4(q_rec[:, :64], torch.full_like(q_rec[:, 64:68], 127)).numpy().astype(np.float32)
     kv = Q.dequantize_mxfp4(k_rec[:, :64], torch.full_like(k_rec[:, 64:68], 127)).numpy().astype(np.float32)
     qs = np.exp2(q_rec[:, 64:68].numpy().astype(np.float32) - 127).astype(np.float32)  # [H, 4]
@@ -100,14 +100,13 @@ def index_scores(q_rec: torch.Tensor, w: torch.Tensor, k_rec: torch.Tensor) -> n
         sc = (qs[:, g:g + 1] * ks[None, :, g]).astype(np.float32)
         acc = (acc + (part * sc).astype(np.float32)).astype(np.float32)
     term = (np.maximum(acc, 0) * w.numpy().astype(np.float32)[:, None]).astype(np.float32)  # [H, C]
-    tot = np.zeros(C, np.float32)
+    pair_sum = np.zeros((8, C), np.float32)
     for tile in range(H // 16):
         t = term[16 * tile:16 * tile + 16]
-        pair = (t[:8] + t[8:]).astype(np.float32)  # heads (i, i+8)
-        for off in (4, 2, 1):
-            idx = np.arange(8) ^ off
-            pair = (pair + pair[idx]).astype(np.float32)
-        tot = (tot + pair[0]).astype(np.float32)
+        pair_sum = (pair_sum + (t[:8] + t[8:]).astype(np.float32)).astype(np.float32)  # heads (i, i+8), tiles in order
+    for off in (4, 2, 1):
+        pair_sum = (pair_sum + pair_sum[np.arange(8) ^ off]).astype(np.float32)
+    tot = pair_sum[0]
     return tot
 
 

@@ -88,25 +88,26 @@ __global__ __launch_bounds__(kScoreWarps * 32) void index_score_kernel(B200Index
         for (int mt = 0; mt < 4; ++mt) {
           float d[4] = {0.f, 0.f, 0.f, 0.f};
           mma_e4m3_16x8x32(d, A[mt][gk][0], A[mt][gk][1], A[mt][gk][2], A[mt][gk][3], b0, b1);
-          // group sums are exact; scale products are exact powers of two; one rounding per add
-          acc[mt][0] = __fadd_rn(acc[mt][0], __fmul_rn(d[0], __fmul_rn(qs[mt][gk][0], k0)));
-          acc[mt][1] = __fadd_rn(acc[mt][1], __fmul_rn(d[1], __fmul_rn(qs[mt][gk][0], k1)));
-          acc[mt][2] = __fadd_rn(acc[mt][2], __fmul_rn(d[2], __fmul_rn(qs[mt][gk][1], k0)));
-          acc[mt][3] = __fadd_rn(acc[mt][3], __fmul_rn(d[3], __fmul_rn(qs[mt][gk][1], k1)));
+          // group sums and the power-of-two scale products are exact, so d * scale is exact and the fused
+          // multiply-add rounds exactly once, like a separate multiply and add would
+          acc[mt][0] = __fmaf_rn(d[0], __fmul_rn(qs[mt][gk][0], k0), acc[mt][0]);
+          acc[mt][1] = __fmaf_rn(d[1], __fmul_rn(qs[mt][gk][0], k1), acc[mt][1]);
+          acc[mt][2] = __fmaf_rn(d[2], __fmul_rn(qs[mt][gk][1], k0), acc[mt][2]);
+          acc[mt][3] = __fmaf_rn(d[3], __fmul_rn(qs[mt][gk][1], k1), acc[mt][3]);
         }
       }
-      // heads: pair (g, g+8), xor tree over g, tiles in order
-      float tot[2] = {0.f, 0.f};
+      // heads: pair (g, g+8) of every tile added in tile order inside the lane, then one xor tree over g
+      float tot[2];
 #pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
+      for (int j = 0; j < 2; ++j) {
+        float v = 0.f;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          float v = __fadd_rn(__fmul_rn(fmaxf(acc[mt][j], 0.f), wh[mt][0]), __fmul_rn(fmaxf(acc[mt][2 + j], 0.f), wh[mt][1]));
-          v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
-          v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
-          v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
-          tot[j] = __fadd_rn(tot[j], v);
-        }
+        for (int mt = 0; mt < 4; ++mt)
+          v = __fadd_rn(v, __fadd_rn(__fmul_rn(fmaxf(acc[mt][j], 0.f), wh[mt][0]), __fmul_rn(fmaxf(acc[mt][2 + j], 0.f), wh[mt][1])));
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+        tot[j] = v;
       }
       if (g == 0) {
         const int key = key0 + kt * 8 + 2 * c;

@@ -1,6 +1,7 @@
 // Sparse MLA decode over the selected FP8 latent entries (flash decoding, split + combine).
 //
-// Split: task = (row, chunk of 64 selected entries), all local heads (16 = one MMA M tile).
+// Split: task = (row, chunk of 64 selected entries); the local heads are taken 16 at a time (one MMA M
+//   tile) over the same gathered entries.
 //   gather the 64 paged records, dequantise e4m3 * scale -> bf16 into shared memory,
 //   S = Q K^T on bf16 tensor cores (k = 512 latent + 64 position dims), split-local softmax
 //   (own max m, sum l of the unrounded probabilities), P rounded to bf16, O = P V with V = the
@@ -39,7 +40,7 @@ struct MlaSmem {
 __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs a) {
   extern __shared__ __align__(16) uint8_t raw[];
   MlaSmem& sm = *reinterpret_cast<MlaSmem*>(raw);
-  const int t = blockIdx.y, chunk = blockIdx.x, hg = blockIdx.z;  // hg: group of 16 heads
+  const int t = blockIdx.y, chunk = blockIdx.x;
   const int H = a.heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
   const int n_sel = a.topk_count[t];
@@ -50,19 +51,6 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
   const int* pages = a.page_table + (size_t)req * a.max_pages;
   const int* sel = a.topk_idx + (size_t)t * a.k + e0;
 
-  // ---- queries: [16][512 latent | 64 position] bf16
-  {
-    const uint4* ql = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_lat) + ((size_t)t * H + hg * kMlaHeads) * kLat);
-    for (int i = threadIdx.x; i < kMlaHeads * kLat / 8; i += 128) {
-      const int h = i / (kLat / 8), v = i % (kLat / 8);
-      *reinterpret_cast<uint4*>(&sm.q[h][v * 8]) = ql[i];
-    }
-    const uint4* qr = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_rope) + ((size_t)t * H + hg * kMlaHeads) * kRope);
-    for (int i = threadIdx.x; i < kMlaHeads * kRope / 8; i += 128) {
-      const int h = i / (kRope / 8), v = i % (kRope / 8);
-      *reinterpret_cast<uint4*>(&sm.q[h][kLat + v * 8]) = qr[i];
-    }
-  }
   // ---- gather + dequantise: warp w takes keys 16w .. 16w+15
   for (int j = 0; j < 16; ++j) {
     const int key = warp * 16 + j;
@@ -88,6 +76,21 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
     dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
     dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
     if (lane < 8) *reinterpret_cast<uint4*>(&sm.rope[key][lane * 8]) = rope16;
+  }
+  // the gathered entries serve every group of 16 heads in turn (hg)
+  for (int hg = 0; hg < H / kMlaHeads; ++hg) {
+  // ---- queries: [16][512 latent | 64 position] bf16
+  {
+    const uint4* ql = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_lat) + ((size_t)t * H + hg * kMlaHeads) * kLat);
+    for (int i = threadIdx.x; i < kMlaHeads * kLat / 8; i += 128) {
+      const int h = i / (kLat / 8), v = i % (kLat / 8);
+      *reinterpret_cast<uint4*>(&sm.q[h][v * 8]) = ql[i];
+    }
+    const uint4* qr = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_rope) + ((size_t)t * H + hg * kMlaHeads) * kRope);
+    for (int i = threadIdx.x; i < kMlaHeads * kRope / 8; i += 128) {
+      const int h = i / (kRope / 8), v = i % (kRope / 8);
+      *reinterpret_cast<uint4*>(&sm.q[h][kLat + v * 8]) = qr[i];
+    }
   }
   __syncthreads();
 
@@ -170,6 +173,8 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
       *reinterpret_cast<uint32_t*>(po + (size_t)(g + 8) * kLat + n0 + 2 * c) = pack_bf16x2(o[2], o[3]);
     }
   }
+  __syncthreads();  // q, p and s are rewritten by the next group of heads
+  }
 }
 
 // grid (heads, rows), 128 threads: 4 latent dims per thread
@@ -206,7 +211,7 @@ cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  dim3 grid(a.max_chunks, a.rows, a.heads / kMlaHeads);
+  dim3 grid(a.max_chunks, a.rows);
   sparse_mla_split_kernel<<<grid, 128, sizeof(MlaSmem), s>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;

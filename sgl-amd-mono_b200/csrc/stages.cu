@@ -251,8 +251,14 @@ __global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a) {
       if (e < E) {
         // chunk sums in chunk order
         const float* parts = a.logit_parts + ((size_t)t * E + e) * nch;
-        float l = __ldcg(parts);
-        for (int ch = 1; ch < nch; ++ch) l = __fadd_rn(l, __ldcg(parts + ch));
+        // (all loads first, so that their L2 latencies overlap; hidden <= 16384 means nch <= 16)
+        float pv[16];
+#pragma unroll
+        for (int ch = 0; ch < 16; ++ch) pv[ch] = ch < nch ? __ldcg(parts + ch) : 0.f;
+        float l = pv[0];
+#pragma unroll
+        for (int ch = 1; ch < 16; ++ch)
+          if (ch < nch) l = __fadd_rn(l, pv[ch]);
         a.logits[(size_t)t * E + e] = l;
         if (a.score_fn == B200MONO_SCORE_SOFTMAX) {
           score[j] = l;
