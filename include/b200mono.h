@@ -388,6 +388,64 @@ typedef struct {
 } B200SparseMlaArgs;
 int b200mono_sparse_mla(const B200SparseMlaArgs* a, void* stream);
 
+/* Dense grouped-query attention of decode / verify rows over a paged bf16 KV cache (64-token pages), causal through
+ * ctx_len and optionally windowed: replaces the split-KV attention stage of
+ * sgl_amd_mono/muse_spark/gfx950/stages/attention.py:264-741 (and the gated-attention layers of the Qwen hybrids);
+ * torch: test/kernels/test_muse_spark_kattn.py:35-67.  P is rounded to bf16, chunk partials (m, l, O) stay f32.
+ * When k_new is set the rows' new K / V are first written to `slots` (slot <= 0: nothing). */
+typedef struct {
+  const void* q;             /* bf16 [rows, q_heads, head_dim], RoPE applied */
+  void* k_cache;             /* bf16 [slots, kv_heads, head_dim] */
+  void* v_cache;             /* bf16 [slots, kv_heads, head_dim] */
+  const void* k_new;         /* bf16 [rows, kv_heads, head_dim] or NULL */
+  const void* v_new;         /* bf16 [rows, kv_heads, head_dim] or NULL */
+  const int32_t* slots;      /* int32 [rows]: cache slot of each row's new token (with k_new) */
+  const int32_t* page_table; /* int32 [requests, max_pages] */
+  const int32_t* req_of_row; /* int32 [rows] */
+  const int32_t* ctx_len;    /* int32 [rows]: keys visible to the row (its position + 1) */
+  float* part_o;             /* f32 [rows, q_heads, max_chunks, head_dim] scratch */
+  float* part_ml;            /* f32 [rows, q_heads, max_chunks, 2] scratch */
+  void* out;                 /* bf16 [rows, q_heads, head_dim] */
+  int32_t rows, q_heads, kv_heads, head_dim; /* head_dim 128 or 256; q_heads / kv_heads <= 16 */
+  int32_t max_pages, max_chunks;             /* max_chunks >= ceil(max ctx_len / 128) */
+  int32_t window;                            /* 0: full causal; else the last `window` keys */
+  float scale;
+} B200GqaArgs;
+int b200mono_gqa_decode(const B200GqaArgs* a, void* stream);
+
+/* Gated delta network core (head dim 128) for decode and verify rows: causal 4-tap convolution + SiLU over the
+ * projected q | k | v columns, gate scalars, the delta-rule recurrence on the f32 state, gated RMSNorm with z and
+ * the per-head FP8 group of the next projection.  tokens > 1 or commit = 0 is the verify form: the window and the
+ * state after every token go to the snapshot buffers and the committed recurrent state is not written; commit = 1
+ * (tokens = 1) is the decode form: state updated in place, f32 conv taps, beta rounded to bf16.  Replaces
+ * _conv_chain_kernel / _delta_chain_kernel (sgl_amd_mono/qwen35_a17b/fp8/gfx950/verify.py:56-233) and the decode
+ * kernels (sgl_amd_mono/qwen35_a17b/fp8/gfx950/gdn.py:95-140,190-281).  Requests with slot < 0 write nothing and
+ * give zero rows. */
+typedef struct {
+  const void* qkvz;          /* bf16 [rows, qkvz_stride]: q (hk*128) | k (hk*128) | v (hv*128) | z (hv*128) */
+  const void* hidden;        /* bf16 [rows, k_in]: the layer's normed input (gate dots) */
+  const void* ba_w;          /* bf16 [2*hv, k_in]: b rows then a rows */
+  const void* conv_w;        /* bf16 [conv_dim, 4], conv_dim = (2*hk + hv) * 128 */
+  const void* conv_bias;     /* bf16 [conv_dim] or NULL */
+  void* conv_state;          /* bf16 [slots, 3, conv_dim]: advanced in place */
+  float* ssm_state;          /* f32 [slots, hv, 128, 128] ([v][k]) */
+  const int32_t* slot;       /* int32 [requests]; < 0: dead request */
+  const int32_t* inter_slot; /* int32 [requests] or NULL; < 0: no snapshots for the request */
+  void* inter_conv;          /* bf16 [islots, tokens, 3, conv_dim] */
+  float* inter_ssm;          /* f32 [islots, tokens, hv, 128, 128] */
+  const float* a_log;        /* f32 [hv] */
+  const float* dt_bias;      /* f32 [hv] */
+  const void* norm_w;        /* bf16 [128] */
+  void* mixed;               /* bf16 [rows, conv_dim] scratch: the convolution's output */
+  void* out;                 /* bf16 [rows, hv*128] */
+  void* out_q;               /* e4m3 [rows, hv*128] */
+  float* out_scale;          /* f32 [rows, hv] */
+  int32_t requests, tokens, hk, hv, k_in, qkvz_stride; /* rows = requests * tokens */
+  int32_t commit, pad_;
+  float scale, eps;
+} B200GdnArgs;
+int b200mono_gdn(const B200GdnArgs* a, void* stream);
+
 /* ------------------------------------------------------------------------
  * The same block for callers that cannot allocate device memory.  This entry
  * point has no counterpart in the reference (its runner always owns a scratch

@@ -146,3 +146,35 @@ def sparse_mla(q_lat: torch.Tensor, q_rope: torch.Tensor, recs: torch.Tensor, sc
     den = sum(l * torch.exp(m - M) for m, l, _ in parts)
     out = sum(o * torch.exp(m - M) for m, _, o in parts) / den
     return out.to(torch.bfloat16)
+
+
+def gqa_attention(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, scale: float, window: int = 0, chunk: int = 128):
+    """One row of dense grouped-query attention: q bf16 [q_heads, d]; K, V bf16 [keys, kv_heads, d] = the row's
+    visible keys in position order (the row's own token last).  Query head h reads KV head h // (q_heads/kv_heads).
+    Causal (windowed: only the last `window` keys) softmax attention with P rounded to bf16 and K / V exact in f32
+    (test/kernels/test_muse_spark_kattn.py:35-67); evaluated per chunk of `chunk` keys with split-local (m, l) and
+    merged as sgl_amd_mono/muse_spark/gfx950/stages/attention.py:606-659 merges its key-split partials.
+    Returns bf16 [q_heads, d]."""
+    Hq, d = q.shape
+    n, Hkv, _ = K.shape
+    G = Hq // Hkv
+    first = max(0, n - window) if window else 0
+    out = torch.zeros(Hq, d)
+    qf = q.float()
+    for h in range(Hq):
+        Kh, Vh = K[:, h // G].float(), V[:, h // G].float()
+        s = (Kh @ qf[h]) * np.float32(scale)
+        s[:first] = float("-inf")
+        ms, ls, os_ = [], [], []
+        for c0 in range((first // chunk) * chunk, n, chunk):
+            sc = s[c0 : c0 + chunk]
+            m = sc.max()
+            p = torch.exp(sc - m)
+            ls.append(p.sum())
+            ms.append(m)
+            os_.append(p.bfloat16().float() @ Vh[c0 : c0 + chunk])
+        M = torch.stack(ms).max()
+        w = torch.exp(torch.stack(ms) - M)
+        den = (torch.stack(ls) * w).sum()
+        out[h] = (torch.stack(os_) * w[:, None]).sum(0) / den
+    return out.bfloat16()

@@ -62,7 +62,8 @@ int b200mono_abi_sizes(int32_t* out, int32_t capacity) {
                            (int32_t)sizeof(B200AllReduceArgs),
                            (int32_t)sizeof(B200KvWriteArgs),   (int32_t)sizeof(B200QPostArgs),
                            (int32_t)sizeof(B200IdxQPostArgs),  (int32_t)sizeof(B200IndexScoreArgs),
-                           (int32_t)sizeof(B200TopkArgs),      (int32_t)sizeof(B200SparseMlaArgs)};
+                           (int32_t)sizeof(B200TopkArgs),      (int32_t)sizeof(B200SparseMlaArgs),
+                           (int32_t)sizeof(B200GqaArgs),      (int32_t)sizeof(B200GdnArgs)};
   const int32_t n = (int32_t)(sizeof(sizes) / sizeof(sizes[0]));
   for (int32_t i = 0; i < n && i < capacity; ++i) out[i] = sizes[i];
   return n;
@@ -237,6 +238,38 @@ int b200mono_sparse_mla(const B200SparseMlaArgs* a, void* stream) {
               aligned(a->o_lat, 16),
           "sparse_mla: pointers must be 16-byte aligned");
   return cuda_status(launch_sparse_mla(*a, (cudaStream_t)stream), "sparse_mla");
+}
+
+int b200mono_gqa_decode(const B200GqaArgs* a, void* stream) {
+  REQUIRE(a && a->q && a->k_cache && a->v_cache && a->page_table && a->req_of_row && a->ctx_len && a->part_o &&
+              a->part_ml && a->out,
+          "gqa_decode: null pointer");
+  REQUIRE((a->k_new == nullptr) == (a->v_new == nullptr) && (!a->k_new || a->slots), "gqa_decode: k_new, v_new and slots go together");
+  REQUIRE(a->rows >= 1 && (a->head_dim == 128 || a->head_dim == 256) && a->kv_heads >= 1 && a->q_heads >= a->kv_heads &&
+              a->q_heads % a->kv_heads == 0 && a->q_heads / a->kv_heads <= 16 && a->max_pages >= 1 && a->max_chunks >= 1 &&
+              a->max_chunks <= (a->max_pages + 1) / 2 && a->window >= 0,
+          "gqa_decode: rows=%d q_heads=%d kv_heads=%d head_dim=%d max_pages=%d max_chunks=%d", a->rows, a->q_heads,
+          a->kv_heads, a->head_dim, a->max_pages, a->max_chunks);
+  REQUIRE(aligned(a->q, 16) && aligned(a->k_cache, 16) && aligned(a->v_cache, 16) && aligned(a->part_o, 8) &&
+              (!a->k_new || (aligned(a->k_new, 16) && aligned(a->v_new, 16))),
+          "gqa_decode: q, caches and new rows must be 16-byte aligned");
+  return cuda_status(launch_gqa(*a, (cudaStream_t)stream), "gqa_decode");
+}
+
+int b200mono_gdn(const B200GdnArgs* a, void* stream) {
+  REQUIRE(a && a->qkvz && a->hidden && a->ba_w && a->conv_w && a->conv_state && a->ssm_state && a->slot && a->a_log &&
+              a->dt_bias && a->norm_w && a->mixed && a->out && a->out_q && a->out_scale,
+          "gdn: null pointer");
+  REQUIRE(a->requests >= 1 && a->tokens >= 1 && a->tokens <= 16 && a->hk >= 1 && a->hv >= a->hk && a->hv % a->hk == 0 &&
+              a->k_in >= 8 && a->k_in % 8 == 0 && a->qkvz_stride >= (2 * a->hk + 2 * a->hv) * 128,
+          "gdn: requests=%d tokens=%d hk=%d hv=%d k_in=%d qkvz_stride=%d", a->requests, a->tokens, a->hk, a->hv, a->k_in,
+          a->qkvz_stride);
+  REQUIRE(a->commit == 0 || a->tokens == 1, "gdn: commit=1 is the decode form (tokens=1), got tokens=%d", a->tokens);
+  REQUIRE(a->commit == 1 || !a->inter_slot || (a->inter_conv && a->inter_ssm), "gdn: inter_slot without snapshot buffers");
+  REQUIRE(aligned(a->hidden, 16) && aligned(a->ba_w, 16) && aligned(a->conv_w, 8) && aligned(a->ssm_state, 16) &&
+              (!a->inter_ssm || aligned(a->inter_ssm, 16)) && aligned(a->out_q, 4),
+          "gdn: hidden, ba_w, states must be 16-byte aligned");
+  return cuda_status(launch_gdn(*a, (cudaStream_t)stream), "gdn");
 }
 
 int b200mono_moe_ffn_layout(int32_t rows, int32_t hidden, int32_t inter, int32_t experts, int32_t topk,

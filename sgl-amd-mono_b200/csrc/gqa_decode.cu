@@ -1,0 +1,220 @@
+// Dense grouped-query attention for decode / verify rows over a paged bf16 KV cache (flash decoding).
+//
+// Split: task = (row, KV head, chunk of 128 consecutive keys).  The chunk's K and V rows (two 64-token
+// pages) are staged in shared memory with 16-byte loads; the G query heads that share the KV head are
+// the MMA M rows (G <= 16); S = Q K^T and O = P V run on bf16 tensor cores, the softmax is split-local
+// (own max m, sum l of the unrounded probabilities, P rounded to bf16), partial O is kept in f32.
+// Combine: per (row, query head) the partials are merged with w_c = exp(m_c - M) / sum_c l_c exp(m_c - M).
+// Keys at positions >= ctx_len[row] are masked, so a verify row sees exactly its causal prefix; with window > 0
+// only the last `window` of them.
+#include "common.cuh"
+#include "launch.h"
+
+namespace b200mono {
+
+constexpr int kGqaChunk = 128;
+
+__device__ __forceinline__ void mma_bf16_k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
+template <int D>
+struct GqaSmem {
+  __nv_bfloat16 k[kGqaChunk][D + 8];
+  __nv_bfloat16 v[kGqaChunk][D + 8];
+  __nv_bfloat16 q[16][D + 8];
+  __nv_bfloat16 p[16][kGqaChunk + 8];
+  float s[16][kGqaChunk];
+};
+
+template <int D>
+__global__ __launch_bounds__(128) void gqa_split_kernel(B200GqaArgs a) {
+  extern __shared__ __align__(16) uint8_t raw[];
+  GqaSmem<D>& sm = *reinterpret_cast<GqaSmem<D>*>(raw);
+  const int chunk = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int n_keys = a.ctx_len[t];
+  const int key0 = chunk * kGqaChunk;
+  const int first = a.window > 0 ? max(0, n_keys - a.window) : 0;  // sliding window: keys first .. n_keys-1
+  if (key0 >= n_keys || key0 + kGqaChunk <= first) return;
+  const int n_here = min(kGqaChunk, n_keys - key0);
+  const int G = a.q_heads / a.kv_heads;
+  const int* pages = a.page_table + (size_t)a.req_of_row[t] * a.max_pages;
+  constexpr int VPR = D / 8;  // 16-byte vectors per row
+
+  // queries of this KV head's group (rows past G are zero)
+  for (int i = threadIdx.x; i < 16 * VPR; i += 128) {
+    const int h = i / VPR, v = i % VPR;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (h < G)
+      val = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q) + ((size_t)t * a.q_heads + kvh * G + h) * D)[v];
+    *reinterpret_cast<uint4*>(&sm.q[h][v * 8]) = val;
+  }
+  // K and V rows of the chunk
+  for (int i = threadIdx.x; i < kGqaChunk * VPR; i += 128) {
+    const int key = i / VPR, v = i % VPR;
+    uint4 kk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+    if (key < n_here) {
+      const int pos = key0 + key;
+      const size_t slot = (size_t)pages[pos >> 6] * 64 + (pos & 63);
+      const size_t off = (slot * a.kv_heads + kvh) * D;
+      kk = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.k_cache) + off)[v];
+      vv = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.v_cache) + off)[v];
+    }
+    *reinterpret_cast<uint4*>(&sm.k[key][v * 8]) = kk;
+    *reinterpret_cast<uint4*>(&sm.v[key][v * 8]) = vv;
+  }
+  __syncthreads();
+
+  // S = Q K^T: warp w owns keys 32w .. 32w+31 (four tiles of 8)
+  {
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+    const int n0 = warp * 32;
+#pragma unroll 4
+    for (int k0 = 0; k0 < D; k0 += 16) {
+      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sm.q[g][k0 + 2 * c]);
+      const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sm.q[g + 8][k0 + 2 * c]);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sm.q[g][k0 + 2 * c + 8]);
+      const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sm.q[g + 8][k0 + 2 * c + 8]);
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&sm.k[n0 + nt * 8 + g][k0 + 2 * c]);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&sm.k[n0 + nt * 8 + g][k0 + 2 * c + 8]);
+        mma_bf16_k16(s[nt], a0, a1, a2, a3, b0, b1);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = g + ((i & 2) ? 8 : 0), col = n0 + nt * 8 + 2 * c + (i & 1);
+        sm.s[row][col] = (col < n_here && key0 + col >= first) ? s[nt][i] * a.scale : -INFINITY;
+      }
+  }
+  __syncthreads();
+  // split-local softmax: warp w owns heads 4w .. 4w+3; lane covers keys lane, lane+32, lane+64, lane+96
+  for (int hh = 0; hh < 4; ++hh) {
+    const int h = warp * 4 + hh;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = sm.s[h][lane + 32 * j];
+    const float m = warp_max(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])));
+    float l = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float p = __expf(v[j] - m);
+      l += p;
+      sm.p[h][lane + 32 * j] = __float2bfloat16_rn(p);
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    if (lane == 0 && h < G) {
+      float* ml = a.part_ml + ((((size_t)t * a.q_heads + kvh * G + h) * a.max_chunks) + chunk) * 2;
+      ml[0] = m;
+      ml[1] = l;
+    }
+  }
+  __syncthreads();
+  // O = P V: warp w owns dims [w*D/4, (w+1)*D/4)
+  {
+    uint32_t pa[kGqaChunk / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < kGqaChunk / 16; ++ks) {
+      pa[ks][0] = *reinterpret_cast<const uint32_t*>(&sm.p[g][ks * 16 + 2 * c]);
+      pa[ks][1] = *reinterpret_cast<const uint32_t*>(&sm.p[g + 8][ks * 16 + 2 * c]);
+      pa[ks][2] = *reinterpret_cast<const uint32_t*>(&sm.p[g][ks * 16 + 2 * c + 8]);
+      pa[ks][3] = *reinterpret_cast<const uint32_t*>(&sm.p[g + 8][ks * 16 + 2 * c + 8]);
+    }
+#pragma unroll 2
+    for (int nt = 0; nt < D / 32; ++nt) {
+      const int n0 = warp * (D / 4) + nt * 8;
+      float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ks = 0; ks < kGqaChunk / 16; ++ks) {
+        uint32_t b0, b1;
+        ldsm_x2_trans(b0, b1, (uint32_t)__cvta_generic_to_shared(&sm.v[ks * 16 + (lane & 15)][n0]));
+        mma_bf16_k16(o, pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b0, b1);
+      }
+      // rows g and g+8 are query heads of the group
+      if (g < G) {
+        float* po = a.part_o + ((((size_t)t * a.q_heads + kvh * G + g) * a.max_chunks) + chunk) * D + n0 + 2 * c;
+        po[0] = o[0];
+        po[1] = o[1];
+      }
+      if (g + 8 < G) {
+        float* po = a.part_o + ((((size_t)t * a.q_heads + kvh * G + g + 8) * a.max_chunks) + chunk) * D + n0 + 2 * c;
+        po[0] = o[2];
+        po[1] = o[3];
+      }
+    }
+  }
+}
+
+// grid (q_heads, rows), D threads
+__global__ void gqa_combine_kernel(B200GqaArgs a) {
+  const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x, D = a.head_dim;
+  const int nch = (a.ctx_len[t] + kGqaChunk - 1) / kGqaChunk;
+  const float* ml = a.part_ml + (((size_t)t * a.q_heads + h) * a.max_chunks) * 2;
+  const float* po = a.part_o + (((size_t)t * a.q_heads + h) * a.max_chunks) * D;
+  const int ch0 = a.window > 0 ? max(0, a.ctx_len[t] - a.window) / kGqaChunk : 0;
+  float M = -INFINITY;
+  for (int ch = ch0; ch < nch; ++ch) M = fmaxf(M, ml[2 * ch]);
+  float den = 0.f, acc = 0.f;
+  for (int ch = ch0; ch < nch; ++ch) {
+    const float w = __expf(ml[2 * ch] - M);
+    den += ml[2 * ch + 1] * w;
+    acc += po[(size_t)ch * D + d] * w;
+  }
+  reinterpret_cast<__nv_bfloat16*>(a.out)[((size_t)t * a.q_heads + h) * D + d] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+}
+
+// new tokens' K and V rows into their cache slots (pad rows, slot <= 0, write nothing): grid rows, 128 threads
+__global__ void gqa_kv_write_kernel(B200GqaArgs a) {
+  const int t = blockIdx.x;
+  const int slot = a.slots[t];
+  if (slot <= 0) return;
+  const int n = a.kv_heads * a.head_dim / 8;  // 16-byte vectors per token
+  const uint4* ks = reinterpret_cast<const uint4*>(a.k_new) + (size_t)t * n;
+  const uint4* vs = reinterpret_cast<const uint4*>(a.v_new) + (size_t)t * n;
+  uint4* kd = reinterpret_cast<uint4*>(a.k_cache) + (size_t)slot * n;
+  uint4* vd = reinterpret_cast<uint4*>(a.v_cache) + (size_t)slot * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    kd[i] = ks[i];
+    vd[i] = vs[i];
+  }
+}
+
+template <int D>
+static cudaError_t launch_gqa_d(const B200GqaArgs& a, cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gqa_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(GqaSmem<D>));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  if (a.k_new) gqa_kv_write_kernel<<<a.rows, 128, 0, s>>>(a);
+  dim3 grid(a.max_chunks, a.kv_heads, a.rows);
+  gqa_split_kernel<D><<<grid, 128, sizeof(GqaSmem<D>), s>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  dim3 grid2(a.q_heads, a.rows);
+  gqa_combine_kernel<<<grid2, D, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gqa(const B200GqaArgs& a, cudaStream_t s) {
+  return a.head_dim == 128 ? launch_gqa_d<128>(a, s) : launch_gqa_d<256>(a, s);
+}
+
+}  // namespace b200mono

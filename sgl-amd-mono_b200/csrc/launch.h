@@ -30,6 +30,8 @@ cudaError_t launch_idx_q_post(const B200IdxQPostArgs& a, cudaStream_t s);
 cudaError_t launch_index_score(const B200IndexScoreArgs& a, cudaStream_t s);
 cudaError_t launch_topk(const B200TopkArgs& a, cudaStream_t s);
 cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s);
+cudaError_t launch_gqa(const B200GqaArgs& a, cudaStream_t s);
+cudaError_t launch_gdn(const B200GdnArgs& a, cudaStream_t s);
 cudaError_t launch_allreduce(const B200AllReduceArgs& a, cudaStream_t s);
 
 // device buffer for timeline marks (null: tracing off), set by b200mono_set_timeline

@@ -1,0 +1,90 @@
+"""Generate tests/golden/gdn_reference.npz by running the reference's own Triton GDN kernels (verify chains and the
+decode kernel of qwen35_a17b/fp8/gfx950) on CPU under the Triton interpreter, on f32 tensors (the interpreter has
+no bf16 arithmetic).  Run once where the reference checkout is present:
+
+    TRITON_INTERPRET=1 python tests/golden/make_golden_gdn.py /path/to/reference
+
+Inputs come from oracle.gdn.make_case (seeded), so only the reference's outputs are stored; the large recurrent
+snapshots are stored sub-sampled (every 8th row and column) together with their f64 sums.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+
+os.environ["TRITON_INTERPRET"] = "1"
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+CASE = dict(seed=11, requests=3, tokens=4, hk=1, hv=2, k_in=256, dead=(1,), no_snapshot=(2,))
+DECODE = dict(seed=12, requests=3, tokens=1, hk=1, hv=2, k_in=256, dead=(0,))
+SCALE, EPS = 128 ** -0.5, 1e-6
+
+
+def main(ref: str) -> None:
+    sys.path.insert(0, ref)
+    import triton
+    from oracle import gdn as O
+    from sgl_amd_mono.qwen35_a17b.fp8.gfx950 import gdn as RG
+    from sgl_amd_mono.qwen35_a17b.fp8.gfx950 import verify as RV
+
+    out = {}
+    f32 = torch.float32
+    qkvz, hidden, w, st, step = O.make_case(act=f32, **CASE)
+    R, T, hk, hv, k_in = CASE["requests"], CASE["tokens"], CASE["hk"], CASE["hv"], CASE["k_in"]
+    rows, D = R * T, O.D
+    conv_dim = 2 * hk * D + hv * D
+    mixed = torch.zeros(rows, conv_dim)
+    cs, ic = st["conv_state"], st["inter_conv"]
+    RV._conv_chain_kernel[(R, triton.cdiv(conv_dim, 256))](
+        qkvz, qkvz.stride(0), w["conv_w"], w["conv_w"], cs, cs.stride(0), cs.stride(2), cs.stride(1), step["slot"],
+        ic, ic.stride(0), ic.stride(1), ic.stride(3), ic.stride(2), step["inter_slot"], mixed, mixed.stride(0),
+        C=conv_dim, T=T, BLOCK=256, HAS_BIAS=False)
+    o = torch.zeros(rows, hv * D)
+    oq = torch.zeros(rows, hv * D)
+    osc = torch.zeros(hv, rows)
+    ss, iss = st["ssm_state"], st["inter_ssm"]
+    ss0 = ss.clone()
+    RV._delta_chain_kernel[(R, hv)](
+        mixed, mixed.stride(0), qkvz, qkvz.stride(0), hidden, hidden.stride(0), w["ba_w"], w["ba_w"].stride(0),
+        ss, ss.stride(0), ss.stride(1), ss.stride(2), ss.stride(3), step["slot"],
+        iss, iss.stride(0), iss.stride(1), iss.stride(2), iss.stride(3), iss.stride(4), step["inter_slot"],
+        w["a_log"], w["dt_bias"], w["norm_w"], o, o.stride(0), oq, oq.stride(0), osc, rows, SCALE, EPS, 448.0, 1 / 448.0,
+        HK=hk, HV=hv, D=D, K_IN=k_in, T=T, THRESHOLD=20.0, ROUND=False)
+    assert torch.equal(ss, ss0)  # verify leaves the committed state alone
+    out.update(v_mixed=mixed.numpy(), v_conv_state=cs.numpy(), v_inter_conv=ic.numpy(), v_out=o.numpy(), v_out_q=oq.numpy(),
+               v_scale=osc.T.contiguous().numpy(), v_inter_ssm_sub=iss[..., ::8, ::8].contiguous().numpy(),
+               v_inter_ssm_sum=iss.double().sum((-1, -2)).numpy())
+
+    # decode: one token per request, state committed in place, beta rounded to bf16 (gdn.py:225-281); its conv
+    # lives inside the projection launch there, so the conv output of the oracle's decode rule is the kernel's input
+    qkvz, hidden, w, st, step = O.make_case(act=f32, **DECODE)
+    R, hk, hv, k_in = DECODE["requests"], DECODE["hk"], DECODE["hv"], DECODE["k_in"]
+    conv_dim = 2 * hk * D + hv * D
+    mixed = O.conv_chain(qkvz, w["conv_w"], None, st["conv_state"], step["slot"], step["inter_slot"], None, 1, conv_dim,
+                         verify=False, act=f32)
+    o = torch.zeros(R, hv * D)
+    oq = torch.zeros(R, hv * D)
+    osc = torch.zeros(hv, R)
+    ss = st["ssm_state"]
+    vals = dict(conv_ptr=mixed, stride_conv=mixed.stride(0), qkvz_ptr=qkvz, stride_qkvz=qkvz.stride(0), hidden_ptr=hidden,
+                stride_hidden=hidden.stride(0), ba_w_ptr=w["ba_w"], stride_ba_w=w["ba_w"].stride(0), state_ptr=ss,
+                stride_s_slot=ss.stride(0), stride_s_head=ss.stride(1), stride_s_v=ss.stride(2), stride_s_k=ss.stride(3),
+                idx_ptr=step["slot"], a_log_ptr=w["a_log"], dt_bias_ptr=w["dt_bias"], norm_w_ptr=w["norm_w"], out_ptr=o,
+                stride_out=o.stride(0), q_ptr=oq, stride_q=oq.stride(0), q_scale_ptr=osc, rows=R, scale=SCALE, eps=EPS,
+                fp8_max=448.0, inv_fp8_max=1 / 448.0, HK=hk, HV=hv, D=D, K_IN=k_in, THRESHOLD=20.0)
+    RG._delta_kernel[(R, hv)](**vals)
+    out.update(d_out=o.numpy(), d_scale=osc.T.contiguous().numpy(), d_state_sub=ss[..., ::8, ::8].contiguous().numpy(),
+               d_state_sum=ss.double().sum((-1, -2)).numpy())
+    path = os.path.join(HERE, "gdn_reference.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, {k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

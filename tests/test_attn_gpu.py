@@ -215,3 +215,69 @@ def test_sparse_mla_against_oracle(lib, n_sel):
         ref = A.sparse_mla(q_lat[t], q_rope[t], cache[slots], scale)
         e = rel(o[t], ref)
         assert e < 1e-2, (t, e)  # bf16 output of an FP8-cache attention; differences: exp and summation order
+
+
+def _gqa_case(lens, tokens_per_request, q_heads, kv_heads, d, seed):
+    """Requests with `lens[r]` keys after the step; request r's rows sit at its last tokens_per_request positions."""
+    g = torch.Generator().manual_seed(seed)
+    R, L = len(lens), tokens_per_request
+    rows = R * L
+    max_pages = (max(lens) + 63) // 64
+    max_pages += max_pages & 1
+    n_pages = R * max_pages + 1
+    k_cache = torch.randn(n_pages * 64, kv_heads, d, generator=g).bfloat16()
+    v_cache = torch.randn(n_pages * 64, kv_heads, d, generator=g).bfloat16()
+    table = (torch.randperm(n_pages - 1, generator=g)[: R * max_pages] + 1).view(R, max_pages).to(torch.int32)
+    q = torch.randn(rows, q_heads, d, generator=g).bfloat16()
+    k_new = torch.randn(rows, kv_heads, d, generator=g).bfloat16()
+    v_new = torch.randn(rows, kv_heads, d, generator=g).bfloat16()
+    req = torch.arange(R).repeat_interleave(L).to(torch.int32)
+    ctx = torch.tensor([lens[r] - L + j + 1 for r in range(R) for j in range(L)], dtype=torch.int32)
+    pos = (ctx - 1).long()
+    slots = (table[req.long(), pos // 64].long() * 64 + pos % 64).to(torch.int32)
+    return dict(q=q, k_cache=k_cache, v_cache=v_cache, k_new=k_new, v_new=v_new, table=table, req=req, ctx=ctx,
+                slots=slots, max_pages=max_pages)
+
+
+@pytest.mark.parametrize("lens,L,hq,hkv,d,window", [
+    ([300], 1, 8, 1, 128, 0),
+    ([3000, 2200], 4, 8, 1, 128, 2047),
+    ([5000, 17, 700, 2049], 2, 16, 2, 128, 0),
+    ([8192, 4100], 4, 16, 2, 256, 0),
+    ([1500, 129, 128, 127], 1, 4, 2, 256, 100),
+])
+def test_gqa_decode_against_oracle(lib, lens, L, hq, hkv, d, window):
+    c = _gqa_case(lens, L, hq, hkv, d, seed=len(lens) + d)
+    rows = c["q"].shape[0]
+    chunks = (max(lens) + 127) // 128
+    kc, vc = c["k_cache"].to(DEV), c["v_cache"].to(DEV)
+    part_o = torch.full((rows, hq, chunks, d), float("nan"), device=DEV)
+    part_ml = torch.full((rows, hq, chunks, 2), float("nan"), device=DEV)
+    out = torch.full((rows, hq, d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scale = d ** -0.5
+    lib.call("gqa_decode", cabi.fill("B200GqaArgs", q=c["q"].to(DEV), k_cache=kc, v_cache=vc, k_new=c["k_new"].to(DEV),
+                                     v_new=c["v_new"].to(DEV), slots=c["slots"].to(DEV), page_table=c["table"].to(DEV),
+                                     req_of_row=c["req"].to(DEV), ctx_len=c["ctx"].to(DEV), part_o=part_o, part_ml=part_ml,
+                                     out=out, rows=rows, q_heads=hq, kv_heads=hkv, head_dim=d, max_pages=c["max_pages"],
+                                     max_chunks=chunks, window=window, scale=scale), stream())
+    torch.cuda.synchronize()
+    # the cache after the step: new rows in their slots, nothing else touched (bit-exact)
+    k_ref, v_ref = c["k_cache"].clone(), c["v_cache"].clone()
+    k_ref[c["slots"].long()] = c["k_new"]
+    v_ref[c["slots"].long()] = c["v_new"]
+    assert torch.equal(kc.cpu(), k_ref) and torch.equal(vc.cpu(), v_ref)
+    for t in range(rows):
+        n = int(c["ctx"][t])
+        pos = torch.arange(n)
+        sl = c["table"][int(c["req"][t]), pos // 64].long() * 64 + pos % 64
+        ref = A.gqa_attention(c["q"][t], k_ref[sl], v_ref[sl], scale, window)
+        e = rel(out[t], ref)
+        assert e < 5e-3, (t, n, e)  # differences: exp implementation and f32 summation order
+
+
+def test_gqa_decode_refuses_bad_shapes(lib):
+    z = torch.zeros(64, device=DEV)
+    a = cabi.fill("B200GqaArgs", q=z, k_cache=z, v_cache=z, page_table=z, req_of_row=z, ctx_len=z, part_o=z, part_ml=z,
+                  out=z, rows=1, q_heads=8, kv_heads=1, head_dim=64, max_pages=2, max_chunks=1, scale=1.0)
+    with pytest.raises(cabi.B200MonoError, match="head_dim=64"):
+        lib.call("gqa_decode", a, stream())
