@@ -44,6 +44,10 @@ enum {
   B200MONO_SCORE_SIGMOID_BIAS = 1,
   B200MONO_SCORE_SQRT_SOFTPLUS_BIAS = 2
 };
+enum {
+  B200MONO_INDEX_TCGEN05 = 0,
+  B200MONO_INDEX_MMA_SYNC = 1
+};
 
 int b200mono_abi_version(void);
 const char* b200mono_last_error(void);
@@ -353,6 +357,9 @@ typedef struct {
   const int32_t* ctx_len;    /* int32 [rows]: keys visible to the row (its position + 1) */
   float* scores;             /* f32 [rows, score_stride] out */
   int32_t rows, max_pages, max_ctx, score_stride;
+  uint32_t* status;          /* optional: set non-zero (7 << 16 | cta) when a wait on the tensor core gave up */
+  int32_t variant;           /* B200MONO_INDEX_*: 0 = tcgen05 tiles of 128 keys, 1 = warp-level mma.sync kernel */
+  int32_t pad_;
 } B200IndexScoreArgs;
 int b200mono_index_score(const B200IndexScoreArgs* a, void* stream);
 

@@ -120,6 +120,7 @@ __global__ __launch_bounds__(kScoreWarps * 32) void index_score_kernel(B200Index
 }
 
 cudaError_t launch_index_score(const B200IndexScoreArgs& a, cudaStream_t s) {
+  if (a.variant != B200MONO_INDEX_MMA_SYNC) return launch_index_score_tc(a, s);
   const int keys_per_cta = kScoreWarps * kPagesPerWarp * 64;
   dim3 grid((a.max_ctx + keys_per_cta - 1) / keys_per_cta, a.rows);
   index_score_kernel<<<grid, kScoreWarps * 32, 0, s>>>(a);

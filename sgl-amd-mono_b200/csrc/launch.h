@@ -28,6 +28,7 @@ cudaError_t launch_kv_write(const B200KvWriteArgs& a, cudaStream_t s);
 cudaError_t launch_q_post(const B200QPostArgs& a, cudaStream_t s);
 cudaError_t launch_idx_q_post(const B200IdxQPostArgs& a, cudaStream_t s);
 cudaError_t launch_index_score(const B200IndexScoreArgs& a, cudaStream_t s);
+cudaError_t launch_index_score_tc(const B200IndexScoreArgs& a, cudaStream_t s);
 cudaError_t launch_topk(const B200TopkArgs& a, cudaStream_t s);
 cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s);
 cudaError_t launch_gqa(const B200GqaArgs& a, cudaStream_t s);

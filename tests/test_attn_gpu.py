@@ -127,17 +127,22 @@ def _keys_of(cache, table, req, n):
     return torch.cat([codes, scales], 1)
 
 
-@pytest.mark.parametrize("ctx", [[17, 64, 65, 1000], [4096, 5000, 1, 2047, 2048, 2049, 9000, 300], [65536, 40000]])
-def test_index_scores_bit_exact(lib, ctx):
+@pytest.mark.parametrize("variant", [0, 1])  # tcgen05 tiles of 128 keys; warp-level mma.sync
+@pytest.mark.parametrize("ctx", [[17, 64, 65, 1000], [4096, 5000, 1, 2047, 2048, 2049, 9000, 300], [65536, 40000],
+                                 [127, 128, 129, 1]])
+def test_index_scores_bit_exact(lib, ctx, variant):
     rows = len(ctx)
     q_rec, w, cache, table, max_pages = _index_case(rows, ctx, seed=rows)
     stride = max_pages * 64
     scores = torch.full((rows, stride), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
     lib.call("index_score", cabi.fill("B200IndexScoreArgs", q_rec=q_rec.to(DEV), w=w.to(DEV), idx_cache=cache.to(DEV),
                                       page_table=table.to(DEV), req_of_row=i32(list(range(rows))), ctx_len=i32(ctx),
-                                      scores=scores, rows=rows, max_pages=max_pages, max_ctx=max(ctx), score_stride=stride),
+                                      scores=scores, rows=rows, max_pages=max_pages, max_ctx=max(ctx), score_stride=stride,
+                                      status=status, variant=variant),
              stream())
     torch.cuda.synchronize()
+    assert int(status) == 0
     got = scores.cpu().numpy()
     for t in range(rows):
         ref = A.index_scores(q_rec[t], w[t], _keys_of(cache, table, t, ctx[t]))
