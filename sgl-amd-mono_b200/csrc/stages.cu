@@ -161,60 +161,61 @@ cudaError_t launch_quant128(const B200Quant128Args& a, cudaStream_t s) {
 }
 
 // ------------------------------------------------------------------ router
-// Phase 1 (all CTAs): warp per (expert, 1024-column chunk): per-chunk partial logits for
-// every row in the stated order, enough independent loads in flight to stream the gate
-// matrix at full rate.
-// Phase 2 (the CTA that arrives last): warp per row, score + exact top-k by
-// (key descending, expert id ascending) + weights; then the union of picked
-// experts in ascending id order and, per union entry, which slot of which row
-// picked it.
+// Phase 1 (all CTAs): CTA = (1024-column chunk, eight experts).  The chunk of every row is staged in shared
+// memory with all loads in flight at once (16 rows per pass), each warp streams its expert's 2 KB of the
+// chunk and writes the per-chunk partial logits in the stated order.
+// Phase 2 (the CTA that arrives last), eight rows at a time: all threads add the chunk partials in chunk
+// order and score them (every load independent), then a warp per row picks the exact top-k by
+// (key descending, expert id ascending) with two warp reductions per pick, then the weights; finally the
+// union of picked experts in ascending id order and, per union entry, which slot of which row picked it.
 constexpr int kMaxExperts = 512;
 
-template <int MAXT>
-__global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a) {
+template <int MAXT, int SLOTS>  // SLOTS = experts a lane owns at most (experts <= 32 * SLOTS)
+__global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a, unsigned long long* trace) {
+  constexpr int PASS = MAXT < 16 ? MAXT : 16;  // rows staged per pass
+  __shared__ __align__(16) uint8_t s_raw[32768];  // phase 1: x chunk [PASS][128] uint4; phase 2: keys and scores [8][512]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned long long t_start = trace ? globaltimer_ns() : 0ull;
+  if (trace && blockIdx.x == 0 && tid == 0) trace[0] = t_start;
   const int T = a.rows, E = a.experts, H = a.hidden;
-  // Phase 1: warp per (expert, 1024-column chunk); four independent 16-byte loads per lane.
   const int nch = (H + 1023) >> 10;
   {
-    const int item = blockIdx.x * 8 + warp;
-    if (item < E * nch) {
-      const int e = item / nch, ch = item % nch;
-      float acc[MAXT];
+    const int ch = blockIdx.x % nch, e = (blockIdx.x / nch) * 8 + warp;
+    const int nv = H >> 3;  // 16-byte vectors per row
+    uint4 wv[4];
 #pragma unroll
-      for (int t = 0; t < MAXT; ++t) acc[t] = 0.f;
-      const uint4* wrow = reinterpret_cast<const uint4*>(a.gate_w) + (size_t)e * (H >> 3);
-      const uint4* xb = reinterpret_cast<const uint4*>(a.x);
-      uint4 wv[4];
+    for (int i = 0; i < 4; ++i) {
+      const int v = ch * 128 + lane + 32 * i;
+      wv[i] = (e < E && v < nv) ? ld_stream_u4(reinterpret_cast<const uint4*>(a.gate_w) + (size_t)e * nv + v) : make_uint4(0, 0, 0, 0);
+    }
+    uint4 (*s_x)[128] = reinterpret_cast<uint4 (*)[128]>(s_raw);
+    for (int t0 = 0; t0 < T; t0 += PASS) {
+      __syncthreads();
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int v = ch * 128 + lane + 32 * i;
-        wv[i] = v < (H >> 3) ? ld_stream_u4(wrow + v) : make_uint4(0, 0, 0, 0);
+      for (int i = 0; i < PASS / 2; ++i) {  // PASS * 128 vectors over 256 threads
+        const int idx = tid + 256 * i, t = t0 + (idx >> 7), v = ch * 128 + (idx & 127);
+        s_x[idx >> 7][idx & 127] = (t < T && v < nv) ? reinterpret_cast<const uint4*>(a.x)[(size_t)t * nv + v] : make_uint4(0, 0, 0, 0);
       }
+      __syncthreads();
+      if (e < E) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int v = ch * 128 + lane + 32 * i;
-        if (v >= (H >> 3)) continue;
-        const uint32_t ww[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
+        for (int tt = 0; tt < PASS; ++tt) {
+          if (t0 + tt < T) {  // warp-uniform
+            float acc = 0.f;
 #pragma unroll
-        for (int t = 0; t < MAXT; ++t) {
-          if (t < T) {
-            uint4 xv = xb[(size_t)t * (H >> 3) + v];
-            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+            for (int i = 0; i < 4; ++i) {
+              const uint4 xv = s_x[tt][lane + 32 * i];
+              const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, ww[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              // bf16 x bf16 is exact in f32, so each step is one rounding
-              acc[t] = __fadd_rn(acc[t], __fmul_rn(bf16_lo(xw[j]), bf16_lo(ww[j])));
-              acc[t] = __fadd_rn(acc[t], __fmul_rn(bf16_hi(xw[j]), bf16_hi(ww[j])));
+              for (int j = 0; j < 4; ++j) {
+                // bf16 x bf16 is exact in f32, so each fused step rounds once, like a separate multiply and add
+                acc = __fmaf_rn(bf16_lo(xw[j]), bf16_lo(ww[j]), acc);
+                acc = __fmaf_rn(bf16_hi(xw[j]), bf16_hi(ww[j]), acc);
+              }
             }
+            acc = warp_sum_tree(acc);
+            if (lane == 0) a.logit_parts[((size_t)(t0 + tt) * E + e) * nch + ch] = acc;
           }
-        }
-      }
-#pragma unroll
-      for (int t = 0; t < MAXT; ++t) {
-        if (t < T) {
-          float v = warp_sum_tree(acc[t]);
-          if (lane == 0) a.logit_parts[((size_t)t * E + e) * nch + ch] = v;
         }
       }
     }
@@ -233,92 +234,106 @@ __global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a) {
   }
   __syncthreads();
   if (!s_last) return;
+  if (trace && tid == 0) {
+    trace[1] = t_start;
+    trace[2] = globaltimer_ns();
+  }
   __threadfence();
   for (int e = tid; e < E; e += 256) s_flag[e] = 0;
-  __syncthreads();
 
   const int K = a.topk;
-  for (int t = warp; t < T; t += 8) {
-    // lane owns experts lane, lane+32, ...
-    float score[kMaxExperts / 32];
-    uint32_t key[kMaxExperts / 32];
-    unsigned taken = 0;
+  uint32_t (*s_key)[kMaxExperts] = reinterpret_cast<uint32_t (*)[kMaxExperts]>(s_raw);
+  float (*s_score)[kMaxExperts] = reinterpret_cast<float (*)[kMaxExperts]>(s_raw + 8 * kMaxExperts * 4);
+  for (int t0 = 0; t0 < T; t0 += 8) {
+    const int nt = min(8, T - t0);
+    __syncthreads();
+    // logits and keys of nt rows: chunk sums in chunk order (hidden <= 16384 means nch <= 16); four (row, expert)
+    // pairs per step so that their partials' loads from L2 are all in flight together
+    for (int idx0 = tid; idx0 < nt * E; idx0 += 4 * 256) {
+      float pv[4][16];
 #pragma unroll
-    for (int j = 0; j < kMaxExperts / 32; ++j) {
-      const int e = lane + 32 * j;
-      score[j] = 0.f;
-      key[j] = 0;
-      if (e < E) {
-        // chunk sums in chunk order
-        const float* parts = a.logit_parts + ((size_t)t * E + e) * nch;
-        // (all loads first, so that their L2 latencies overlap; hidden <= 16384 means nch <= 16)
-        float pv[16];
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + 256 * u;
+        const float* parts = a.logit_parts + ((size_t)t0 * E + idx) * nch;  // rows of a batch are consecutive
 #pragma unroll
-        for (int ch = 0; ch < 16; ++ch) pv[ch] = ch < nch ? __ldcg(parts + ch) : 0.f;
-        float l = pv[0];
+        for (int ch = 0; ch < 16; ++ch)
+          if (ch < 8 || nch > 8) pv[u][ch] = (idx < nt * E && ch < nch) ? __ldcg(parts + ch) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = idx0 + 256 * u;
+        if (idx >= nt * E) break;
+        const int tt = idx / E, e = idx - tt * E, t = t0 + tt;
+        float l = pv[u][0];
 #pragma unroll
         for (int ch = 1; ch < 16; ++ch)
-          if (ch < nch) l = __fadd_rn(l, pv[ch]);
+          if (ch < nch) l = __fadd_rn(l, pv[u][ch]);
         a.logits[(size_t)t * E + e] = l;
         if (a.score_fn == B200MONO_SCORE_SOFTMAX) {
-          score[j] = l;
-          key[j] = radix_key(l);
+          s_score[tt][e] = l;
+          s_key[tt][e] = radix_key(l);
         } else {
-          float sg = det_sigmoid(l);
-          score[j] = sg;
-          key[j] = radix_key(a.bias ? __fadd_rn(sg, a.bias[e]) : sg);
+          const float sg = det_sigmoid(l);
+          s_score[tt][e] = sg;
+          s_key[tt][e] = radix_key(a.bias ? __fadd_rn(sg, a.bias[e]) : sg);
         }
+      }
+    }
+    __syncthreads();
+    if (trace && tid == 0 && t0 == 0) trace[3] = globaltimer_ns();
+    if (warp < nt) {
+      const int t = t0 + warp;
+      // lane owns experts lane, lane + 32, ...
+      uint32_t key[SLOTS];
+      unsigned taken = 0;
+#pragma unroll
+      for (int j = 0; j < SLOTS; ++j) {
+        const int e = lane + 32 * j;
+        key[j] = e < E ? s_key[warp][e] : 0u;
+        if (e >= E) taken |= 1u << j;
+      }
+      float my_raw = 0.f;  // lane kk keeps the raw score of rank kk
+      int my_id = 0;
+      for (int kk = 0; kk < K; ++kk) {
+        // the lane's best: largest key, the smallest expert id among equals (strict > keeps the earlier slot)
+        uint32_t bk = 0;
+        int bj = -1;
+#pragma unroll
+        for (int j = 0; j < SLOTS; ++j)
+          if (!(taken & (1u << j)) && (bj < 0 || key[j] > bk)) {
+            bk = key[j];
+            bj = j;
+          }
+        const uint32_t top = __reduce_max_sync(0xffffffffu, bj >= 0 ? bk : 0u);
+        const uint32_t e = __reduce_min_sync(0xffffffffu, (bj >= 0 && bk == top) ? (uint32_t)(lane + 32 * bj) : 0xffffffffu);
+        if (lane == (int)(e & 31u)) taken |= 1u << (e >> 5);
+        if (lane == kk) {
+          my_raw = s_score[warp][e];
+          my_id = (int)e;
+        }
+      }
+      // weights
+      float wgt;
+      if (a.score_fn == B200MONO_SCORE_SOFTMAX) {
+        const float top = __shfl_sync(0xffffffffu, my_raw, 0);
+        wgt = lane < K ? det_exp(__fsub_rn(my_raw, top)) : 0.f;
       } else {
-        taken |= 1u << j;
+        wgt = lane < K ? my_raw : 0.f;
       }
-    }
-    float my_raw = 0.f;  // lane kk keeps the raw score of rank kk
-    int my_id = 0;
-    for (int kk = 0; kk < K; ++kk) {
-      unsigned long long best = 0;
-#pragma unroll
-      for (int j = 0; j < kMaxExperts / 32; ++j) {
-        if (!(taken & (1u << j))) {
-          unsigned long long cand =
-              ((unsigned long long)key[j] << 32) | (uint32_t)(0xffffffffu - (uint32_t)(lane + 32 * j));
-          best = cand > best ? cand : best;
-        }
+      float sum = 0.f;
+      for (int kk = 0; kk < K; ++kk) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, wgt, kk));
+      wgt = __fdiv_rn(wgt, sum);
+      if (a.score_fn != B200MONO_SCORE_SOFTMAX) wgt = __fmul_rn(wgt, a.route_scale);
+      if (lane < K) {
+        a.topk_ids[(size_t)t * K + lane] = my_id;
+        a.topk_w[(size_t)t * K + lane] = wgt;
+        s_ids[t * 16 + lane] = my_id;
+        s_flag[my_id] = 1;
       }
-      const unsigned long long win = warp_max_u64(best);
-      const int e = (int)(0xffffffffu - (uint32_t)(win & 0xffffffffu));
-      float raw = 0.f;
-#pragma unroll
-      for (int j = 0; j < kMaxExperts / 32; ++j)
-        if (lane + 32 * j == e) {
-          taken |= 1u << j;
-          raw = score[j];
-        }
-      raw = __shfl_sync(0xffffffffu, raw, e & 31);
-      if (lane == kk) {
-        my_raw = raw;
-        my_id = e;
-      }
-    }
-    // weights
-    float wgt;
-    if (a.score_fn == B200MONO_SCORE_SOFTMAX) {
-      const float top = __shfl_sync(0xffffffffu, my_raw, 0);
-      wgt = lane < K ? det_exp(__fsub_rn(my_raw, top)) : 0.f;
-    } else {
-      wgt = lane < K ? my_raw : 0.f;
-    }
-    float sum = 0.f;
-    for (int kk = 0; kk < K; ++kk) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, wgt, kk));
-    wgt = __fdiv_rn(wgt, sum);
-    if (a.score_fn != B200MONO_SCORE_SOFTMAX) wgt = __fmul_rn(wgt, a.route_scale);
-    if (lane < K) {
-      a.topk_ids[(size_t)t * K + lane] = my_id;
-      a.topk_w[(size_t)t * K + lane] = wgt;
-      s_ids[t * 16 + lane] = my_id;
-      s_flag[my_id] = 1;
     }
   }
   __syncthreads();
+  if (trace && tid == 0) trace[4] = globaltimer_ns();
   if (warp == 0) {
     int base = 0;
     for (int e0 = 0; e0 < E; e0 += 32) {
@@ -350,17 +365,29 @@ __global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a) {
   if (tid == 0) {
     *a.union_count = UT;
     *a.counter = 0;
+    if (trace) trace[5] = globaltimer_ns();
   }
 }
 
 cudaError_t launch_router(const B200RouterArgs& a, cudaStream_t s) {
-  const unsigned grid = (unsigned)((a.experts * ((a.hidden + 1023) / 1024) + 7) / 8);
-  if (a.rows <= 8)
-    router_kernel<8><<<grid, 256, 0, s>>>(a);
-  else if (a.rows <= 16)
-    router_kernel<16><<<grid, 256, 0, s>>>(a);
-  else
-    router_kernel<32><<<grid, 256, 0, s>>>(a);
+  const unsigned grid = (unsigned)(((a.experts + 7) / 8) * ((a.hidden + 1023) / 1024));
+  // timeline marks (when tracing is on): six words after the persistent kernels' 4 * 256 * 8
+  unsigned long long* tr = timeline_buffer() ? (unsigned long long*)timeline_buffer() + 8192 : nullptr;
+  if (a.experts <= 256) {
+    if (a.rows <= 8)
+      router_kernel<8, 8><<<grid, 256, 0, s>>>(a, tr);
+    else if (a.rows <= 16)
+      router_kernel<16, 8><<<grid, 256, 0, s>>>(a, tr);
+    else
+      router_kernel<32, 8><<<grid, 256, 0, s>>>(a, tr);
+  } else {
+    if (a.rows <= 8)
+      router_kernel<8, 16><<<grid, 256, 0, s>>>(a, tr);
+    else if (a.rows <= 16)
+      router_kernel<16, 16><<<grid, 256, 0, s>>>(a, tr);
+    else
+      router_kernel<32, 16><<<grid, 256, 0, s>>>(a, tr);
+  }
   return cudaGetLastError();
 }
 
