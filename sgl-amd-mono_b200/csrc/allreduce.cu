@@ -37,6 +37,7 @@ __device__ __forceinline__ size_t inbox_chunk(const ArP& p, int parity, int src,
 }
 
 __global__ __launch_bounds__(256) void allreduce_kernel(ArP p) {
+  pdl_enter();
   const uint32_t epoch = ld_relaxed_gpu_u32(p.words);
   const uint32_t tag = epoch + 1;
   const int parity = (int)(epoch & 1u);
@@ -138,7 +139,7 @@ cudaError_t launch_allreduce(const B200AllReduceArgs& a, cudaStream_t s) {
   int grid = (int)((nchunk + 255) / 256);
   if (grid > 128) grid = 128;  // all CTAs must be resident: a CTA waits for peers while holding its SM
   if (grid < 1) grid = 1;
-  allreduce_kernel<<<grid, 256, 0, s>>>(p);
+  launch_pdl(allreduce_kernel, grid, 256, 0, s, p);
   return cudaGetLastError();
 }
 

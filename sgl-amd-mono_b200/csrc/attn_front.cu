@@ -38,6 +38,7 @@ __device__ __forceinline__ uint32_t mxfp4_lane(float v, uint32_t& e8m0) {
 // One CTA of 128 threads per row.  Warps 0..3 each quantise one 32-dim group of the index key;
 // warp 0 also copies the latent record, warp 1 rotates the key's position dims.
 __global__ __launch_bounds__(128) void kv_write_kernel(B200KvWriteArgs a) {
+  pdl_enter();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int slot = a.slots[t];
   if (slot <= 0) return;  // pad row: writes nothing
@@ -79,7 +80,7 @@ __global__ __launch_bounds__(128) void kv_write_kernel(B200KvWriteArgs a) {
 }
 
 cudaError_t launch_kv_write(const B200KvWriteArgs& a, cudaStream_t s) {
-  kv_write_kernel<<<a.rows, 128, 0, s>>>(a);
+  launch_pdl(kv_write_kernel, a.rows, 128, 0, s, a);
   return cudaGetLastError();
 }
 
@@ -87,6 +88,7 @@ cudaError_t launch_kv_write(const B200KvWriteArgs& a, cudaStream_t s) {
 // warp per (row, head): q [rows, heads*192] bf16 -> qn_q e4m3 [rows, heads*128], qn_scale f32 [rows, heads],
 // q_rope bf16 [rows, heads*64].
 __global__ __launch_bounds__(256) void q_post_kernel(B200QPostArgs a) {
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int item = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (item >= a.rows * a.heads) return;
@@ -110,7 +112,7 @@ __global__ __launch_bounds__(256) void q_post_kernel(B200QPostArgs a) {
 
 cudaError_t launch_q_post(const B200QPostArgs& a, cudaStream_t s) {
   const int items = a.rows * a.heads;
-  q_post_kernel<<<(items + 7) / 8, 256, 0, s>>>(a);
+  launch_pdl(q_post_kernel, (items + 7) / 8, 256, 0, s, a);
   return cudaGetLastError();
 }
 
@@ -118,6 +120,7 @@ cudaError_t launch_q_post(const B200QPostArgs& a, cudaStream_t s) {
 // warp per (row, index head): qi [rows, heads*128] bf16 -> q_rec u8 [rows, heads, 68] (64 code bytes, 4 scale
 // bytes), and w f32 [rows, heads] = bf16 head weight * weight_scale.
 __global__ __launch_bounds__(256) void idx_q_post_kernel(B200IdxQPostArgs a) {
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int item = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (item >= a.rows * a.heads) return;
@@ -154,7 +157,7 @@ __global__ __launch_bounds__(256) void idx_q_post_kernel(B200IdxQPostArgs a) {
 
 cudaError_t launch_idx_q_post(const B200IdxQPostArgs& a, cudaStream_t s) {
   const int items = a.rows * a.heads;
-  idx_q_post_kernel<<<(items + 7) / 8, 256, 0, s>>>(a);
+  launch_pdl(idx_q_post_kernel, (items + 7) / 8, 256, 0, s, a);
   return cudaGetLastError();
 }
 

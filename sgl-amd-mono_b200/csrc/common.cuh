@@ -39,6 +39,16 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return f32_to_bf16_bits(lo) | (f32_to_bf16_bits(hi) << 16);
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// First statement of every kernel.  launch_dependents lets the next kernel in the stream be scheduled as soon as
+// every CTA of this grid is running (its CTAs then sit in their own wait), which takes the launch latency off the
+// critical path; wait returns when the previous kernel in the stream has completed and its writes are visible.
+// Both are no-ops for a kernel launched without the programmatic-serialization attribute.
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- e4m3 helpers
 // RNE, saturating to +-448 (never NaN for finite input).
 __device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float a, float b, float c, float d) {

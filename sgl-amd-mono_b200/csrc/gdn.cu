@@ -16,6 +16,7 @@ namespace b200mono {
 constexpr int kD = 128;
 
 __global__ __launch_bounds__(256) void conv_chain_kernel(B200GdnArgs a) {
+  pdl_enter();
   const int req = blockIdx.x;
   const int col = blockIdx.y * 256 + threadIdx.x;
   const int conv_dim = (2 * a.hk + a.hv) * kD;
@@ -98,6 +99,7 @@ __device__ __forceinline__ float block_max(float v, float* buf /* [8] */) {
 }
 
 __global__ __launch_bounds__(256, 2) void delta_chain_kernel(B200GdnArgs a) {
+  pdl_enter();
   __shared__ __align__(16) float s_q[kD], s_k[kD], s_v[kD], s_z[kD], s_o[kD];
   __shared__ float s_red[32];
   const int req = blockIdx.x, hv = blockIdx.y, tid = threadIdx.x;
@@ -248,9 +250,9 @@ __global__ __launch_bounds__(256, 2) void delta_chain_kernel(B200GdnArgs a) {
 cudaError_t launch_gdn(const B200GdnArgs& a, cudaStream_t s) {
   const int conv_dim = (2 * a.hk + a.hv) * kD;
   dim3 g1(a.requests, (conv_dim + 255) / 256);
-  conv_chain_kernel<<<g1, 256, 0, s>>>(a);
+  launch_pdl(conv_chain_kernel, g1, 256, 0, s, a);
   dim3 g2(a.requests, a.hv);
-  delta_chain_kernel<<<g2, 256, 0, s>>>(a);
+  launch_pdl(delta_chain_kernel, g2, 256, 0, s, a);
   return cudaGetLastError();
 }
 

@@ -26,6 +26,7 @@ struct GemvP {
 // R == 1: y[t, n] plain store.  R == 2: SwiGLU of (gate row n, up row n + rowset).
 template <int R, int NT>
 __global__ __launch_bounds__(256) void gemv_kernel(GemvP p) {
+  pdl_enter();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
   const int rtw = 8 / p.ks;
   const int rt_local = warp / p.ks, ksl = warp % p.ks;
@@ -129,11 +130,11 @@ static int pick_ks(int KB) {
 template <int R>
 static cudaError_t launch_gemv_r(const GemvP& p, dim3 grid, cudaStream_t s) {
   if (p.rows <= 8)
-    gemv_kernel<R, 1><<<grid, 256, 0, s>>>(p);
+    launch_pdl(gemv_kernel<R, 1>, grid, 256, 0, s, p);
   else if (p.rows <= 16)
-    gemv_kernel<R, 2><<<grid, 256, 0, s>>>(p);
+    launch_pdl(gemv_kernel<R, 2>, grid, 256, 0, s, p);
   else
-    gemv_kernel<R, 4><<<grid, 256, 0, s>>>(p);
+    launch_pdl(gemv_kernel<R, 4>, grid, 256, 0, s, p);
   return cudaGetLastError();
 }
 
@@ -194,6 +195,7 @@ cudaError_t launch_moe_up(const B200MoeUpArgs& a, cudaStream_t s) {
 // The combine then walks the slots in order with a bf16 rounding at each add.
 template <int NT, bool HALF>
 __global__ __launch_bounds__(256) void moe_down_kernel(B200MoeDownArgs a) {
+  pdl_enter();
   extern __shared__ float contrib[];  // [topk+1][rows][RB]
   constexpr int RB = HALF ? 8 : 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
@@ -248,11 +250,11 @@ __global__ __launch_bounds__(256) void moe_down_kernel(B200MoeDownArgs a) {
 template <bool HALF>
 static cudaError_t launch_down_h(const B200MoeDownArgs& a, dim3 grid, size_t smem, cudaStream_t s) {
   if (a.rows <= 8)
-    moe_down_kernel<1, HALF><<<grid, 256, smem, s>>>(a);
+    launch_pdl(moe_down_kernel<1, HALF>, grid, 256, smem, s, a);
   else if (a.rows <= 16)
-    moe_down_kernel<2, HALF><<<grid, 256, smem, s>>>(a);
+    launch_pdl(moe_down_kernel<2, HALF>, grid, 256, smem, s, a);
   else
-    moe_down_kernel<4, HALF><<<grid, 256, smem, s>>>(a);
+    launch_pdl(moe_down_kernel<4, HALF>, grid, 256, smem, s, a);
   return cudaGetLastError();
 }
 

@@ -36,6 +36,7 @@ struct GqaSmem {
 
 template <int D>
 __global__ __launch_bounds__(128) void gqa_split_kernel(B200GqaArgs a) {
+  pdl_enter();
   extern __shared__ __align__(16) uint8_t raw[];
   GqaSmem<D>& sm = *reinterpret_cast<GqaSmem<D>*>(raw);
   const int chunk = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
@@ -163,6 +164,7 @@ __global__ __launch_bounds__(128) void gqa_split_kernel(B200GqaArgs a) {
 
 // grid (q_heads, rows), D threads
 __global__ void gqa_combine_kernel(B200GqaArgs a) {
+  pdl_enter();
   const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x, D = a.head_dim;
   const int nch = (a.ctx_len[t] + kGqaChunk - 1) / kGqaChunk;
   const float* ml = a.part_ml + (((size_t)t * a.q_heads + h) * a.max_chunks) * 2;
@@ -181,6 +183,7 @@ __global__ void gqa_combine_kernel(B200GqaArgs a) {
 
 // new tokens' K and V rows into their cache slots (pad rows, slot <= 0, write nothing): grid rows, 128 threads
 __global__ void gqa_kv_write_kernel(B200GqaArgs a) {
+  pdl_enter();
   const int t = blockIdx.x;
   const int slot = a.slots[t];
   if (slot <= 0) return;
@@ -203,13 +206,13 @@ static cudaError_t launch_gqa_d(const B200GqaArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  if (a.k_new) gqa_kv_write_kernel<<<a.rows, 128, 0, s>>>(a);
+  if (a.k_new) launch_pdl(gqa_kv_write_kernel, a.rows, 128, 0, s, a);
   dim3 grid(a.max_chunks, a.kv_heads, a.rows);
-  gqa_split_kernel<D><<<grid, 128, sizeof(GqaSmem<D>), s>>>(a);
+  launch_pdl(gqa_split_kernel<D>, grid, 128, sizeof(GqaSmem<D>), s, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dim3 grid2(a.q_heads, a.rows);
-  gqa_combine_kernel<<<grid2, D, 0, s>>>(a);
+  launch_pdl(gqa_combine_kernel, grid2, D, 0, s, a);
   return cudaGetLastError();
 }
 

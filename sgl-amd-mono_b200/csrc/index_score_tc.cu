@@ -84,6 +84,7 @@ constexpr int kMaxRows = 64;
 }  // namespace
 
 __global__ __launch_bounds__(128, 4) void index_score_tc_kernel(B200IndexScoreArgs a) {
+  pdl_enter();
   __shared__ __align__(128) uint8_t s_keys[8 * kTileKeys * 16];  // MMA operand: [k chunk 8][key 128][16 B]
   __shared__ __align__(128) uint8_t s_q[8 * kHeads * 16];        // MMA operand: [k chunk 8][head 64][16 B]
   __shared__ __align__(128) uint8_t s_raw[kRing][kRawTile];      // as in the cache: page 0 codes | page 1 codes | scales 0 | scales 1
@@ -304,7 +305,7 @@ cudaError_t launch_index_score_tc(const B200IndexScoreArgs& a, cudaStream_t s) {
   int grid = 4 * sms;
   if (grid * kMaxLocalTiles < bound) grid = (bound + kMaxLocalTiles - 1) / kMaxLocalTiles;
   if (grid > bound) grid = bound;
-  index_score_tc_kernel<<<grid, 128, 0, s>>>(a);
+  launch_pdl(index_score_tc_kernel, grid, 128, 0, s, a);
   return cudaGetLastError();
 }
 

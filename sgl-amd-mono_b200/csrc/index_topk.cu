@@ -33,6 +33,7 @@ constexpr int kScoreWarps = 4;
 // Slot mapping inside a 32-dim group: MMA k-slot 4c+j <-> dim 8c+j, slot 16+4c+j <-> dim 8c+4+j, on both
 // operands, so a lane's operand words are the low / high half of one aligned 4-byte load of packed codes.
 __global__ __launch_bounds__(kScoreWarps * 32) void index_score_kernel(B200IndexScoreArgs a) {
+  pdl_enter();
   __shared__ __align__(16) uint8_t s_page[kScoreWarps][4352];
   const int t = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
   const int n_keys = a.ctx_len[t];
@@ -123,7 +124,7 @@ cudaError_t launch_index_score(const B200IndexScoreArgs& a, cudaStream_t s) {
   if (a.variant != B200MONO_INDEX_MMA_SYNC) return launch_index_score_tc(a, s);
   const int keys_per_cta = kScoreWarps * kPagesPerWarp * 64;
   dim3 grid((a.max_ctx + keys_per_cta - 1) / keys_per_cta, a.rows);
-  index_score_kernel<<<grid, kScoreWarps * 32, 0, s>>>(a);
+  launch_pdl(index_score_kernel, grid, kScoreWarps * 32, 0, s, a);
   return cudaGetLastError();
 }
 
@@ -150,6 +151,7 @@ __device__ __forceinline__ void for_keys(const float* sc, int n, int tid, F&& f)
 }
 
 __global__ __launch_bounds__(1024) void topk_kernel(B200TopkArgs a) {
+  pdl_enter();
   __shared__ unsigned int hist[256];
   // per-warp histograms (score exponents cluster in a few digits); after the select the same storage
   // holds, per (1024-key chunk, warp), the taken counts and then their prefixes
@@ -305,7 +307,7 @@ __device__ __forceinline__ uint32_t dsmem_ld_u32(const void* local, uint32_t ran
 }
 
 __global__ __cluster_dims__(kTopkCluster, 1, 1) __launch_bounds__(1024) void topk_cluster_kernel(B200TopkArgs a) {
-  __shared__ unsigned int whist[32][256];
+  pdl_enter();
   __shared__ unsigned int hist[2][256];      // local histogram, double-buffered across passes
   __shared__ unsigned int s_tot[2];          // this CTA's (above, equal) totals
   __shared__ unsigned int s_cnt[kTopkPer * 32][2], s_pre[kTopkPer * 32][2];
@@ -330,23 +332,21 @@ __global__ __cluster_dims__(kTopkCluster, 1, 1) __launch_bounds__(1024) void top
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
     const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-    for (int i = tid; i < 32 * 256; i += 1024) (&whist[0][0])[i] = 0;
+    // local histogram of this pass, straight into the buffer the peers will read: lanes with the same digit
+    // elect one to add their count (scores cluster in a few digits), warps without a candidate skip the match
+    unsigned int* hl = hist[pass & 1];
+    if (tid < 256) hl[tid] = 0;
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < kTopkPer; ++j) {
       const int i = base + j * 1024 + tid;
       unsigned digit = 256u;
       if (i < n && (key[j] & mask) == prefix) digit = (key[j] >> shift) & 0xffu;
-      const unsigned peers = __match_any_sync(0xffffffffu, digit);
-      if (digit < 256u && lane == __ffs(peers) - 1) whist[warp][digit] += (unsigned)__popc(peers);
-      __syncwarp();
-    }
-    __syncthreads();
-    unsigned int* hl = hist[pass & 1];
-    if (tid < 256) {
-      unsigned c = 0;
-      for (int w = 0; w < 32; ++w) c += whist[w][tid];
-      hl[tid] = c;
+      const unsigned act = __ballot_sync(0xffffffffu, digit < 256u);
+      if (digit < 256u) {
+        const unsigned peers = __match_any_sync(act, digit);
+        if (lane == __ffs(peers) - 1) atomicAdd(&hl[digit], (unsigned)__popc(peers));
+      }
     }
     cluster_sync_all();  // every CTA's local histogram of this pass is complete (and visible)
     // the cluster-wide histogram, summed by every CTA for itself; the buffer of this pass is not
@@ -447,9 +447,9 @@ __global__ __cluster_dims__(kTopkCluster, 1, 1) __launch_bounds__(1024) void top
 cudaError_t launch_topk(const B200TopkArgs& a, cudaStream_t s) {
   if (a.score_stride <= kTopkCluster * kTopkPer * 1024) {  // a row fits one cluster's registers
     dim3 grid(kTopkCluster, a.rows);
-    topk_cluster_kernel<<<grid, 1024, 0, s>>>(a);
+    launch_pdl(topk_cluster_kernel, grid, 1024, 0, s, a);
   } else {
-    topk_kernel<<<a.rows, 1024, 0, s>>>(a);
+    launch_pdl(topk_kernel, a.rows, 1024, 0, s, a);
   }
   return cudaGetLastError();
 }

@@ -35,6 +35,24 @@ cudaError_t launch_gqa(const B200GqaArgs& a, cudaStream_t s);
 cudaError_t launch_gdn(const B200GdnArgs& a, cudaStream_t s);
 cudaError_t launch_allreduce(const B200AllReduceArgs& a, cudaStream_t s);
 
+// Launch with programmatic stream serialization: the kernel may be scheduled before the previous kernel in the
+// stream has finished; it synchronises with it through pdl_enter() (common.cuh).  Works under stream capture,
+// where it becomes a programmatic dependency edge of the graph.
+template <class... KArgs, class... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // device buffer for timeline marks (null: tracing off), set by b200mono_set_timeline
 void* timeline_buffer();
 

@@ -38,6 +38,7 @@ struct MlaSmem {
 };
 
 __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs a) {
+  pdl_enter();
   extern __shared__ __align__(16) uint8_t raw[];
   MlaSmem& sm = *reinterpret_cast<MlaSmem*>(raw);
   const int t = blockIdx.y, chunk = blockIdx.x;
@@ -51,31 +52,47 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
   const int* pages = a.page_table + (size_t)req * a.max_pages;
   const int* sel = a.topk_idx + (size_t)t * a.k + e0;
 
-  // ---- gather + dequantise: warp w takes keys 16w .. 16w+15
-  for (int j = 0; j < 16; ++j) {
-    const int key = warp * 16 + j;
-    uint4 lat16 = make_uint4(0, 0, 0, 0), rope16 = make_uint4(0, 0, 0, 0);
-    float scale = 0.f;
-    if (key < n_here) {
-      const int pos = sel[key];
-      const size_t slot = (size_t)pages[pos >> 6] * 64 + (pos & 63);
-      const uint8_t* rec = reinterpret_cast<const uint8_t*>(a.kv_cache) + slot * 656;
-      lat16 = reinterpret_cast<const uint4*>(rec)[lane];
-      scale = reinterpret_cast<const float*>(rec + 512)[lane >> 3];
-      if (lane < 8) rope16 = reinterpret_cast<const uint4*>(rec + 528)[lane];
-    }
-    const uint32_t w4[4] = {lat16.x, lat16.y, lat16.z, lat16.w};
-    uint32_t o[8];
+  // ---- gather + dequantise: warp w takes keys 16w .. 16w+15.  Lane j < 16 resolves key j's cache slot (selection
+  // -> page table), then the records are fetched four keys at a time so that their loads overlap.
+  size_t my_slot = 0;
+  if (lane < 16 && warp * 16 + lane < n_here) {
+    const int pos = sel[warp * 16 + lane];
+    my_slot = (size_t)pages[pos >> 6] * 64 + (pos & 63);
+  }
+#pragma unroll 1
+  for (int j0 = 0; j0 < 16; j0 += 4) {
+    uint4 lat16[4], rope16[4];
+    float scale[4];
 #pragma unroll
-    for (int q4 = 0; q4 < 4; ++q4) {
-      const float2 lo = e4m3x2_to_f32x2(w4[q4] & 0xffffu), hi = e4m3x2_to_f32x2(w4[q4] >> 16);
-      o[2 * q4] = pack_bf16x2(lo.x * scale, lo.y * scale);
-      o[2 * q4 + 1] = pack_bf16x2(hi.x * scale, hi.y * scale);
+    for (int u = 0; u < 4; ++u) {
+      const int key = warp * 16 + j0 + u;
+      const size_t slot = __shfl_sync(0xffffffffu, my_slot, j0 + u);
+      lat16[u] = make_uint4(0, 0, 0, 0);
+      rope16[u] = make_uint4(0, 0, 0, 0);
+      scale[u] = 0.f;
+      if (key < n_here) {
+        const uint8_t* rec = reinterpret_cast<const uint8_t*>(a.kv_cache) + slot * 656;
+        lat16[u] = ld_stream_u4(reinterpret_cast<const uint4*>(rec) + lane);
+        scale[u] = __ldg(reinterpret_cast<const float*>(rec + 512) + (lane >> 3));
+        if (lane < 8) rope16[u] = ld_stream_u4(reinterpret_cast<const uint4*>(rec + 528) + lane);
+      }
     }
-    uint4* dst = reinterpret_cast<uint4*>(&sm.lat[key][lane * 16]);
-    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-    if (lane < 8) *reinterpret_cast<uint4*>(&sm.rope[key][lane * 8]) = rope16;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int key = warp * 16 + j0 + u;
+      const uint32_t w4[4] = {lat16[u].x, lat16[u].y, lat16[u].z, lat16[u].w};
+      uint32_t o[8];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const float2 lo = e4m3x2_to_f32x2(w4[q4] & 0xffffu), hi = e4m3x2_to_f32x2(w4[q4] >> 16);
+        o[2 * q4] = pack_bf16x2(lo.x * scale[u], lo.y * scale[u]);
+        o[2 * q4 + 1] = pack_bf16x2(hi.x * scale[u], hi.y * scale[u]);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(&sm.lat[key][lane * 16]);
+      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      if (lane < 8) *reinterpret_cast<uint4*>(&sm.rope[key][lane * 8]) = rope16[u];
+    }
   }
   // the gathered entries serve every group of 16 heads in turn (hg)
   for (int hg = 0; hg < H / kMlaHeads; ++hg) {
@@ -177,25 +194,56 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
   }
 }
 
-// grid (heads, rows), 128 threads: 4 latent dims per thread
+// grid (heads, rows), 128 threads: 4 latent dims per thread.  Lane ch of every warp holds chunk ch's (m, l) and then
+// its merge weight (max_chunks <= 32); the partials of eight chunks are fetched together.
 __global__ __launch_bounds__(128) void sparse_mla_combine_kernel(B200SparseMlaArgs a) {
-  const int h = blockIdx.x, t = blockIdx.y, H = a.heads;
+  pdl_enter();
+  const int h = blockIdx.x, t = blockIdx.y, H = a.heads, lane = threadIdx.x & 31;
   const int n_sel = a.topk_count[t];
   const int nch = (n_sel + kChunkKeys - 1) / kChunkKeys;
   const float* ml = a.part_ml + ((size_t)t * a.max_chunks * H + h) * 2;
-  float M = -INFINITY;
-  for (int ch = 0; ch < nch; ++ch) M = fmaxf(M, ml[(size_t)ch * H * 2]);
-  float den = 0.f;
-  for (int ch = 0; ch < nch; ++ch) den += ml[(size_t)ch * H * 2 + 1] * __expf(ml[(size_t)ch * H * 2] - M);
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
   const __nv_bfloat16* po = reinterpret_cast<const __nv_bfloat16*>(a.part_o) + ((size_t)t * a.max_chunks * H + h) * kLat;
-  for (int ch = 0; ch < nch; ++ch) {
-    const float w = __expf(ml[(size_t)ch * H * 2] - M);
-    const uint2 v = reinterpret_cast<const uint2*>(po + (size_t)ch * H * kLat)[threadIdx.x];
-    acc[0] += bf16_lo(v.x) * w;
-    acc[1] += bf16_hi(v.x) * w;
-    acc[2] += bf16_lo(v.y) * w;
-    acc[3] += bf16_hi(v.y) * w;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float den = 0.f;
+  if (a.max_chunks <= 32) {
+    float m = -INFINITY, l = 0.f;
+    if (lane < nch) {
+      const float2 v = *reinterpret_cast<const float2*>(ml + (size_t)lane * H * 2);
+      m = v.x;
+      l = v.y;
+    }
+    const float M = warp_max(m);
+    const float w_mine = lane < nch ? __expf(m - M) : 0.f;
+    // chunk order, as a scalar loop over chunks would add them
+    for (int ch = 0; ch < nch; ++ch) den += __shfl_sync(0xffffffffu, l * w_mine, ch);
+    for (int ch0 = 0; ch0 < nch; ch0 += 8) {
+      uint2 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        v[u] = ch0 + u < nch ? reinterpret_cast<const uint2*>(po + (size_t)(ch0 + u) * H * kLat)[threadIdx.x] : make_uint2(0, 0);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float w = __shfl_sync(0xffffffffu, w_mine, (ch0 + u) & 31);
+        if (ch0 + u < nch) {
+          acc[0] += bf16_lo(v[u].x) * w;
+          acc[1] += bf16_hi(v[u].x) * w;
+          acc[2] += bf16_lo(v[u].y) * w;
+          acc[3] += bf16_hi(v[u].y) * w;
+        }
+      }
+    }
+  } else {
+    float M = -INFINITY;
+    for (int ch = 0; ch < nch; ++ch) M = fmaxf(M, ml[(size_t)ch * H * 2]);
+    for (int ch = 0; ch < nch; ++ch) den += ml[(size_t)ch * H * 2 + 1] * __expf(ml[(size_t)ch * H * 2] - M);
+    for (int ch = 0; ch < nch; ++ch) {
+      const float w = __expf(ml[(size_t)ch * H * 2] - M);
+      const uint2 v = reinterpret_cast<const uint2*>(po + (size_t)ch * H * kLat)[threadIdx.x];
+      acc[0] += bf16_lo(v.x) * w;
+      acc[1] += bf16_hi(v.x) * w;
+      acc[2] += bf16_lo(v.y) * w;
+      acc[3] += bf16_hi(v.y) * w;
+    }
   }
   const float inv = den > 0.f ? 1.0f / den : 0.f;
   uint2 o;
@@ -212,11 +260,11 @@ cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s) {
     configured = true;
   }
   dim3 grid(a.max_chunks, a.rows);
-  sparse_mla_split_kernel<<<grid, 128, sizeof(MlaSmem), s>>>(a);
+  launch_pdl(sparse_mla_split_kernel, grid, 128, sizeof(MlaSmem), s, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dim3 grid2(a.heads, a.rows);
-  sparse_mla_combine_kernel<<<grid2, 128, 0, s>>>(a);
+  launch_pdl(sparse_mla_combine_kernel, grid2, 128, 0, s, a);
   return cudaGetLastError();
 }
 

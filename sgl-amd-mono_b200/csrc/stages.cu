@@ -19,6 +19,7 @@ namespace b200mono {
 // lanes of one warp.
 template <bool HAS_RES>
 __global__ __launch_bounds__(256) void norm_quant_kernel(B200NormQuantArgs a) {
+  pdl_enter();
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nvec = a.hidden >> 3;
   const uint4* x = reinterpret_cast<const uint4*>(a.x) + (size_t)row * ((a.x_stride ? a.x_stride : a.hidden) >> 3);
@@ -110,14 +111,15 @@ __global__ __launch_bounds__(256) void norm_quant_kernel(B200NormQuantArgs a) {
 
 cudaError_t launch_norm_quant(const B200NormQuantArgs& a, cudaStream_t s) {
   if (a.residual)
-    norm_quant_kernel<true><<<a.rows, 256, 0, s>>>(a);
+    launch_pdl(norm_quant_kernel<true>, a.rows, 256, 0, s, a);
   else
-    norm_quant_kernel<false><<<a.rows, 256, 0, s>>>(a);
+    launch_pdl(norm_quant_kernel<false>, a.rows, 256, 0, s, a);
   return cudaGetLastError();
 }
 
 // ------------------------------------------------------------------ plain per-128 quant
 __global__ __launch_bounds__(256) void quant128_kernel(B200Quant128Args a) {
+  pdl_enter();
   const long long total = (long long)a.rows * (a.cols >> 3);
   const long long v = (long long)blockIdx.x * 256 + threadIdx.x;
   const bool ok = v < total;
@@ -156,7 +158,7 @@ __global__ __launch_bounds__(256) void quant128_kernel(B200Quant128Args a) {
 cudaError_t launch_quant128(const B200Quant128Args& a, cudaStream_t s) {
   const long long total = (long long)a.rows * (a.cols >> 3);
   if (total == 0) return cudaSuccess;
-  quant128_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+  launch_pdl(quant128_kernel, (unsigned)((total + 255) / 256), 256, 0, s, a);
   return cudaGetLastError();
 }
 
@@ -172,6 +174,7 @@ constexpr int kMaxExperts = 512;
 
 template <int MAXT, int SLOTS>  // SLOTS = experts a lane owns at most (experts <= 32 * SLOTS)
 __global__ __launch_bounds__(256) void router_kernel(B200RouterArgs a, unsigned long long* trace) {
+  pdl_enter();
   constexpr int PASS = MAXT < 16 ? MAXT : 16;  // rows staged per pass
   __shared__ __align__(16) uint8_t s_raw[32768];  // phase 1: x chunk [PASS][128] uint4; phase 2: keys and scores [8][512]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -375,18 +378,18 @@ cudaError_t launch_router(const B200RouterArgs& a, cudaStream_t s) {
   unsigned long long* tr = timeline_buffer() ? (unsigned long long*)timeline_buffer() + 8192 : nullptr;
   if (a.experts <= 256) {
     if (a.rows <= 8)
-      router_kernel<8, 8><<<grid, 256, 0, s>>>(a, tr);
+      launch_pdl(router_kernel<8, 8>, grid, 256, 0, s, a, tr);
     else if (a.rows <= 16)
-      router_kernel<16, 8><<<grid, 256, 0, s>>>(a, tr);
+      launch_pdl(router_kernel<16, 8>, grid, 256, 0, s, a, tr);
     else
-      router_kernel<32, 8><<<grid, 256, 0, s>>>(a, tr);
+      launch_pdl(router_kernel<32, 8>, grid, 256, 0, s, a, tr);
   } else {
     if (a.rows <= 8)
-      router_kernel<8, 16><<<grid, 256, 0, s>>>(a, tr);
+      launch_pdl(router_kernel<8, 16>, grid, 256, 0, s, a, tr);
     else if (a.rows <= 16)
-      router_kernel<16, 16><<<grid, 256, 0, s>>>(a, tr);
+      launch_pdl(router_kernel<16, 16>, grid, 256, 0, s, a, tr);
     else
-      router_kernel<32, 16><<<grid, 256, 0, s>>>(a, tr);
+      launch_pdl(router_kernel<32, 16>, grid, 256, 0, s, a, tr);
   }
   return cudaGetLastError();
 }

@@ -50,6 +50,7 @@ struct DownP {
 };
 
 __global__ __launch_bounds__(kDownThreads, 1) void down_stream_kernel(DownP p, const __grid_constant__ CUtensorMap tm_w) {
+  pdl_enter();
   extern __shared__ __align__(128) uint8_t smem[];
   const int K = p.inter, T = p.rows, RB = p.rb, PP = p.pp;
   const int SB = RB * K;  // weights of a stage (a multiple of 128: K % 256 == 0)
@@ -265,6 +266,7 @@ __global__ __launch_bounds__(kDownThreads, 1) void down_stream_kernel(DownP p, c
 // out[t, n] = slots summed in order with a bf16 rounding at every add (+ residual), 8 columns per thread
 __global__ __launch_bounds__(256) void moe_combine_kernel(const __nv_bfloat16* contrib, const __nv_bfloat16* residual,
                                                           __nv_bfloat16* out, int rows, int hidden, int slots) {
+  pdl_enter();
   const int nvec = hidden >> 3;
   const int v = blockIdx.x * 256 + threadIdx.x;
   if (v >= rows * nvec) return;
@@ -356,14 +358,13 @@ cudaError_t launch_moe_down_stream(const B200MoeDownArgs& a, void* contrib, uint
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  down_stream_kernel<<<sms, kDownThreads, (size_t)stages * SB + fixed, s>>>(p, tm_w);
+  launch_pdl(down_stream_kernel, sms, kDownThreads, (size_t)stages * SB + fixed, s, p, tm_w);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || a.skip_combine) return e;
   const int slots = a.topk + (has_shared ? 1 : 0);
   const int nvec = a.rows * (a.hidden / 8);
-  moe_combine_kernel<<<(nvec + 255) / 256, 256, 0, s>>>((const __nv_bfloat16*)contrib,
-                                                       (const __nv_bfloat16*)a.residual, (__nv_bfloat16*)a.out, a.rows,
-                                                       a.hidden, slots);
+  launch_pdl(moe_combine_kernel, (nvec + 255) / 256, 256, 0, s, (const __nv_bfloat16*)contrib,
+             (const __nv_bfloat16*)a.residual, (__nv_bfloat16*)a.out, a.rows, a.hidden, slots);
   return cudaGetLastError();
 }
 

@@ -112,6 +112,7 @@ template <int NT, int MODE>
 __global__ __launch_bounds__(kThreads, 1) void stream_kernel(StreamP p, const __grid_constant__ CUtensorMap tm_w,
                                                              const __grid_constant__ CUtensorMap tm_x,
                                                              const __grid_constant__ CUtensorMap tm_xs) {
+  pdl_enter();
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int SB = stage_bytes<NT>();
   // layout: [stages x SB][red: 2 buffers][barriers]
@@ -358,7 +359,7 @@ static cudaError_t launch_stream_nt(StreamP p, int grid, long long w_rows, cudaS
       !make_map(&tm_xs, CU_TENSOR_MAP_DATA_TYPE_UINT32, p.xs, (uint64_t)p.groups * KB, (uint64_t)p.rows,
                 (uint64_t)p.groups * KB * 4, 8, NT * 8))
     return cudaErrorInvalidValue;
-  stream_kernel<NT, MODE><<<grid, kThreads, smem, s>>>(p, tm_w, tm_x, tm_xs);
+  launch_pdl(stream_kernel<NT, MODE>, grid, kThreads, smem, s, p, tm_w, tm_x, tm_xs);
   return cudaGetLastError();
 }
 
