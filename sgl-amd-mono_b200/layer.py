@@ -127,6 +127,9 @@ class LayerRunner:
         self.attn_part = buf((W, b.hidden), bf)
         self.a = buf((W, b.hidden), bf)       # residual stream after attention
         self.status = buf((4,), i32)
+        self.overlap = True
+        self.side = torch.cuda.Stream(dev)
+        self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
         self.ffn = FfnRunner(
             FfnBuild(width=W, hidden=b.hidden, inter=b.inter // b.tp, experts=b.experts, topk=b.topk, score_fn=1,
                      has_shared=True, route_scale=b.route_scale, eps=b.eps), weights.ffn, dev)
@@ -148,26 +151,40 @@ class LayerRunner:
         self.lib.call("quant128", cabi.fill("B200Quant128Args", x=x, q=q, q_scale=qs, rows=rows, cols=cols, zero_rule=0), self._s)
 
     # ------------------------------------------------------------------ the three parts
-    def k1(self, x: torch.Tensor, step: Step, stream=None):
-        b, w, c, rows = self.b, self.w, self.c, x.shape[0]
-        hl = b.heads_local
-        self._s = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+    def _k1_head(self, x: torch.Tensor, step: Step):
+        """Attention norm, the fused q_a | kv | rope | index-key | head-weight projection, q norm."""
+        b, w, rows = self.b, self.w, x.shape[0]
         self._norm_quant(x, w.attn_norm, self.xq, self.xs, rows, b.hidden)
         self._gemv(w.wa, w.wa_s, self.xq, self.xs, self.ya, rows, YA_COLS, b.hidden)
         self._norm_quant(self.ya, w.q_norm, self.qa_q, self.qa_s, rows, Q_LORA, x_stride=YA_COLS)
+
+    def _k1_index(self, rows: int, step: Step):
+        """The branch the indexer waits for: KV record and index key of the new tokens, index query records."""
+        w, c = self.w, self.c
         self._norm_quant(self.ya[:, COL_KV:], w.kv_norm, self.kv_q, self.kv_s, rows, KV_LORA, x_stride=YA_COLS)
         self.lib.call("kv_write", cabi.fill("B200KvWriteArgs", kv_q=self.kv_q, kv_scale=self.kv_s, ya=self.ya,
                                             positions=step.positions, slots=step.slots, rope_table=c.rope_table,
                                             kv_cache=c.kv, idx_cache=c.idx, rows=rows, ldya=YA_COLS, col_rope=COL_ROPE,
                                             col_idx=COL_IDX), self._s)
+        self._gemv(w.wiq_b, w.wiq_b_s, self.qa_q, self.qa_s, self.qi, rows, IDX_HEADS * IDX_DIM, Q_LORA)
+        self.lib.call("idx_q_post", cabi.fill("B200IdxQPostArgs", qi=self.qi, ya=self.ya, positions=step.positions,
+                                              rope_table=c.rope_table, q_rec=self.q_rec, w=self.iw, rows=rows, heads=IDX_HEADS,
+                                              ldya=YA_COLS, col_w=COL_W, weight_scale=self.b.index_weight_scale), self._s)
+
+    def _k1_query(self, rows: int, step: Step):
+        """The attention queries: q_b, RoPE and per-head quant, absorbed latent queries."""
+        b, w, c = self.b, self.w, self.c
+        hl = b.heads_local
         self._gemv(w.wq_b, w.wq_b_s, self.qa_q, self.qa_s, self.q, rows, hl * 192, Q_LORA)
         self.lib.call("q_post", cabi.fill("B200QPostArgs", q=self.q, positions=step.positions, rope_table=c.rope_table,
                                           qn_q=self.qn_q, qn_scale=self.qn_s, q_rope=self.q_rope, rows=rows, heads=hl), self._s)
         self._gemv(w.w_uk, w.w_uk_s, self.qn_q, self.qn_s, self.q_lat, rows, hl * KV_LORA, NOPE, groups=hl)
-        self._gemv(w.wiq_b, w.wiq_b_s, self.qa_q, self.qa_s, self.qi, rows, IDX_HEADS * IDX_DIM, Q_LORA)
-        self.lib.call("idx_q_post", cabi.fill("B200IdxQPostArgs", qi=self.qi, ya=self.ya, positions=step.positions,
-                                              rope_table=c.rope_table, q_rec=self.q_rec, w=self.iw, rows=rows, heads=IDX_HEADS,
-                                              ldya=YA_COLS, col_w=COL_W, weight_scale=b.index_weight_scale), self._s)
+
+    def k1(self, x: torch.Tensor, step: Step, stream=None):
+        self._s = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        self._k1_head(x, step)
+        self._k1_index(x.shape[0], step)
+        self._k1_query(x.shape[0], step)
 
     def k2i(self, rows: int, step: Step, stream=None):
         self._s = (stream or torch.cuda.current_stream(self.device)).cuda_stream
@@ -210,7 +227,26 @@ class LayerRunner:
         self.reducer.run(contrib, a, out, slots=slots, stream=st)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: Step, stream=None):
-        self.k1(x, step, stream)
-        self.k2i(x.shape[0], step, stream)
-        self.k2(x, out, step, stream)
+        """K1, K2i, K2.  With `overlap` (default) the indexer branch (KV / index records, index queries, scores, top-k)
+        runs on a side stream beside the attention-query branch (q_b, RoPE, W_UK); the two meet before sparse MLA.
+        The fork and join are events, so a CUDA graph captured around this call keeps the two branches parallel."""
+        rows = x.shape[0]
+        main = stream or torch.cuda.current_stream(self.device)
+        if not self.overlap:
+            self.k1(x, step, main)
+            self.k2i(rows, step, main)
+            self.k2(x, out, step, main)
+            return out
+        self._s = main.cuda_stream
+        self._k1_head(x, step)
+        self._fork.record(main)
+        self.side.wait_event(self._fork)
+        self._s = self.side.cuda_stream
+        self._k1_index(rows, step)
+        self.k2i(rows, step, self.side)
+        self._join.record(self.side)
+        self._s = main.cuda_stream
+        self._k1_query(rows, step)
+        main.wait_event(self._join)
+        self.k2(x, out, step, main)
         return out
