@@ -455,6 +455,21 @@ typedef struct {
 } B200GdnArgs;
 int b200mono_gdn(const B200GdnArgs* a, void* stream);
 
+/* Per-32 MXFP8 activation quant (e4m3 values, one E8M0 scale code per 32): replaces quant_mxfp8
+ * (sgl_amd_mono/glm53/gfx950/kernel.py:1740-1783) and put_mxfp8_group[_vllm]
+ * (sgl_amd_mono/deepseek_v41/gfx950/stages/moe.py:169-251); torch: test/kernels/deepseek_v41/check_ffn.py:86-104. */
+enum {
+  B200MONO_MX_AITER = 0, /* code = ceil-pow2 exponent of max(amax, 1e-10) * (1/448), clamped to [1, 254] */
+  B200MONO_MX_VLLM = 1   /* code = ceil-pow2 exponent of max(amax, FLT_MIN) / 448, clamped to [0, 254] */
+};
+typedef struct {
+  const void* x;   /* bf16 [rows, cols], cols a multiple of 32 */
+  void* q;         /* e4m3 [rows, cols] */
+  void* q_scale;   /* u8 [rows, cols/32]: E8M0 codes */
+  int32_t rows, cols, rule, pad_;
+} B200QuantMxfp8Args;
+int b200mono_quant_mxfp8(const B200QuantMxfp8Args* a, void* stream);
+
 /* ------------------------------------------------------------------------
  * The same block for callers that cannot allocate device memory.  This entry
  * point has no counterpart in the reference (its runner always owns a scratch

@@ -63,7 +63,8 @@ int b200mono_abi_sizes(int32_t* out, int32_t capacity) {
                            (int32_t)sizeof(B200KvWriteArgs),   (int32_t)sizeof(B200QPostArgs),
                            (int32_t)sizeof(B200IdxQPostArgs),  (int32_t)sizeof(B200IndexScoreArgs),
                            (int32_t)sizeof(B200TopkArgs),      (int32_t)sizeof(B200SparseMlaArgs),
-                           (int32_t)sizeof(B200GqaArgs),      (int32_t)sizeof(B200GdnArgs)};
+                           (int32_t)sizeof(B200GqaArgs),      (int32_t)sizeof(B200GdnArgs),
+                           (int32_t)sizeof(B200QuantMxfp8Args)};
   const int32_t n = (int32_t)(sizeof(sizes) / sizeof(sizes[0]));
   for (int32_t i = 0; i < n && i < capacity; ++i) out[i] = sizes[i];
   return n;
@@ -254,6 +255,14 @@ int b200mono_gqa_decode(const B200GqaArgs* a, void* stream) {
               (!a->k_new || (aligned(a->k_new, 16) && aligned(a->v_new, 16))),
           "gqa_decode: q, caches and new rows must be 16-byte aligned");
   return cuda_status(launch_gqa(*a, (cudaStream_t)stream), "gqa_decode");
+}
+
+int b200mono_quant_mxfp8(const B200QuantMxfp8Args* a, void* stream) {
+  REQUIRE(a && a->x && a->q && a->q_scale, "quant_mxfp8: null pointer");
+  REQUIRE(a->rows >= 0 && a->cols >= 32 && a->cols % 32 == 0 && (a->rule == B200MONO_MX_AITER || a->rule == B200MONO_MX_VLLM),
+          "quant_mxfp8: rows=%d cols=%d (a multiple of 32) rule=%d", a->rows, a->cols, a->rule);
+  REQUIRE(aligned(a->x, 16) && aligned(a->q, 8), "quant_mxfp8: x 16-byte, q 8-byte aligned");
+  return cuda_status(launch_quant_mxfp8(*a, (cudaStream_t)stream), "quant_mxfp8");
 }
 
 int b200mono_gdn(const B200GdnArgs* a, void* stream) {

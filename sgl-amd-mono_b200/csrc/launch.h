@@ -32,6 +32,7 @@ cudaError_t launch_index_score_tc(const B200IndexScoreArgs& a, cudaStream_t s);
 cudaError_t launch_topk(const B200TopkArgs& a, cudaStream_t s);
 cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s);
 cudaError_t launch_gqa(const B200GqaArgs& a, cudaStream_t s);
+cudaError_t launch_quant_mxfp8(const B200QuantMxfp8Args& a, cudaStream_t s);
 cudaError_t launch_gdn(const B200GdnArgs& a, cudaStream_t s);
 cudaError_t launch_allreduce(const B200AllReduceArgs& a, cudaStream_t s);
 

@@ -162,6 +162,56 @@ cudaError_t launch_quant128(const B200Quant128Args& a, cudaStream_t s) {
   return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ per-32 MXFP8 quant
+// One thread per 8 values, four threads per 32-value group.  The E8M0 code is the biased exponent of the smallest
+// power of two >= amax / 448 (AITER rule: amax floored at 1e-10, multiplied by 1/448, code clamped to [1, 254];
+// vLLM rule: amax floored at FLT_MIN, divided by 448, code clamped to [0, 254]); values are multiplied by 2^(127 - code).
+__global__ __launch_bounds__(256) void quant_mxfp8_kernel(B200QuantMxfp8Args a) {
+  pdl_enter();
+  const long long total = (long long)a.rows * (a.cols >> 3);
+  const long long v = (long long)blockIdx.x * 256 + threadIdx.x;
+  const bool ok = v < total;
+  float y[8];
+  float amax = 0.f;
+  if (ok) {
+    uint4 xv = reinterpret_cast<const uint4*>(a.x)[v];
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      y[2 * j] = bf16_lo(xw[j]);
+      y[2 * j + 1] = bf16_hi(xw[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[j]));
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  if (ok) {
+    const float s = a.rule == B200MONO_MX_AITER ? __fmul_rn(fmaxf(amax, 1e-10f), 1.0f / 448.0f)
+                                                : __fdiv_rn(fmaxf(amax, 1.17549435e-38f), 448.0f);
+    const uint32_t bits = __float_as_uint(s);
+    int code = (int)((bits >> 23) & 0xffu) + ((bits & 0x7fffffu) != 0u ? 1 : 0);
+    code = min(max(code, a.rule == B200MONO_MX_AITER ? 1 : 0), 254);
+    // 2^(127 - code): exponent field 254 - code, which is 0 for code 254 (then 2^-127 is the subnormal 0x00400000)
+    const float inv = code == 254 ? __uint_as_float(0x00400000u) : __uint_as_float((uint32_t)(254 - code) << 23);
+    float q[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) q[j] = fminf(fmaxf(__fmul_rn(y[j], inv), -kFp8Max), kFp8Max);
+    uint2 packed;
+    packed.x = f32x4_to_e4m3x4(q[0], q[1], q[2], q[3]);
+    packed.y = f32x4_to_e4m3x4(q[4], q[5], q[6], q[7]);
+    reinterpret_cast<uint2*>(a.q)[v] = packed;
+    if ((threadIdx.x & 3) == 0) reinterpret_cast<uint8_t*>(a.q_scale)[v >> 2] = (uint8_t)code;
+  }
+}
+
+cudaError_t launch_quant_mxfp8(const B200QuantMxfp8Args& a, cudaStream_t s) {
+  const long long total = (long long)a.rows * (a.cols >> 3);
+  if (total == 0) return cudaSuccess;
+  launch_pdl(quant_mxfp8_kernel, (unsigned)((total + 255) / 256), 256, 0, s, a);
+  return cudaGetLastError();
+}
+
 // ------------------------------------------------------------------ router
 // Phase 1 (all CTAs): CTA = (1024-column chunk, eight experts).  The chunk of every row is staged in shared
 // memory with all loads in flight at once (16 rows per pass), each warp streams its expert's 2 KB of the

@@ -265,3 +265,24 @@ def test_negative_control_scale_error_is_caught(lib):
     r.ffn(x, out)
     torch.cuda.synchronize()
     assert rel(out, good) > 0.5
+
+
+@pytest.mark.parametrize("rule", ["aiter", "vllm"])
+def test_quant_mxfp8_bit_exact(lib, rule):
+    g = torch.Generator().manual_seed(31)
+    x = (torch.randn(9, 512, generator=g) * torch.logspace(-6, 3, 9)[:, None]).bfloat16()
+    x[0, :32] = 0                          # an all-zero group takes the floor of the rule
+    x[1, 32:64] = 0
+    x[1, 32] = 448.0                       # exactly a power of two times 448: no round-up of the exponent
+    x[2, :32] = 0
+    x[2, 5] = 450.0                        # just above: the next power of two
+    x[3, 64:96] = 3.0e38                   # largest codes
+    x[4, 96:128] = 1e-38
+    q = torch.zeros(9, 512, dtype=torch.uint8, device=DEV)
+    sc = torch.zeros(9, 16, dtype=torch.uint8, device=DEV)
+    lib.call("quant_mxfp8", cabi.fill("B200QuantMxfp8Args", x=x.to(DEV), q=q, q_scale=sc, rows=9, cols=512,
+                                      rule=0 if rule == "aiter" else 1), stream())
+    torch.cuda.synchronize()
+    rq, rc = Q.mxfp8_quant(x, rule)
+    assert torch.equal(sc.cpu(), rc)
+    assert torch.equal(q.cpu(), rq.view(torch.uint8))
