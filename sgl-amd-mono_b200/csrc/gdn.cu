@@ -98,16 +98,22 @@ __device__ __forceinline__ float block_max(float v, float* buf /* [8] */) {
   return m;
 }
 
+constexpr int kMaxTokens = 8;  // tokens of a chain handled per pass (longer chains run in passes)
+
+// Phase A: gate scalars and the normalised q / k of every token of the pass (one round of block sums).
+// Phase B: the recurrence, token by token, on the state in registers; snapshots are fire-and-forget stores, so
+//          the memory pipe stays busy while the next token's arithmetic runs.
+// Phase C: gated RMSNorm + FP8 group of every token (one more round of block sums).
 __global__ __launch_bounds__(256, 2) void delta_chain_kernel(B200GdnArgs a) {
   pdl_enter();
-  __shared__ __align__(16) float s_q[kD], s_k[kD], s_v[kD], s_z[kD], s_o[kD];
-  __shared__ float s_red[32];
+  __shared__ __align__(16) float s_q[kMaxTokens][kD], s_k[kMaxTokens][kD], s_v[kMaxTokens][kD], s_o[kMaxTokens][kD];
+  __shared__ float s_red[8 * 4 * kMaxTokens];
+  __shared__ float s_decay[kMaxTokens], s_beta[kMaxTokens];
   const int req = blockIdx.x, hv = blockIdx.y, tid = threadIdx.x;
   const int i = tid >> 1, half = tid & 1;
   const int HK = a.hk, HV = a.hv, T = a.tokens;
   const int kh = hv / (HV / HK);
   const int conv_dim = (2 * HK + HV) * kD;
-  const int rows = a.requests * T;
   const int slot = a.slot[req];
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
   uint8_t* out_q = reinterpret_cast<uint8_t*>(a.out_q);
@@ -122,7 +128,6 @@ __global__ __launch_bounds__(256, 2) void delta_chain_kernel(B200GdnArgs a) {
     }
     return;
   }
-  (void)rows;
   const bool verify = !a.commit;
   const int islot = (verify && a.inter_slot) ? a.inter_slot[req] : -1;
   float* cell = a.ssm_state + (((size_t)slot * HV + hv) * kD + i) * kD;
@@ -136,110 +141,153 @@ __global__ __launch_bounds__(256, 2) void delta_chain_kernel(B200GdnArgs a) {
   const __nv_bfloat16* mixed = reinterpret_cast<const __nv_bfloat16*>(a.mixed);
   const __nv_bfloat16* qkvz = reinterpret_cast<const __nv_bfloat16*>(a.qkvz);
 
-  for (int t = 0; t < T; ++t) {
-    const int row = req * T + t;
-    // gate dots b, a over the hidden row, and the q / k vectors with their square sums
-    float sums[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int t0 = 0; t0 < T; t0 += kMaxTokens) {
+    const int nt = min(kMaxTokens, T - t0);
+    // ---- phase A
+    float sums[4 * kMaxTokens];
+#pragma unroll
+    for (int n = 0; n < 4 * kMaxTokens; ++n) sums[n] = 0.f;
+    float qv[kMaxTokens], kv[kMaxTokens];
     for (int e = tid * 8; e < a.k_in; e += 256 * 8) {
-      const uint4 xv = ld_u4(hidden + (size_t)row * a.k_in + e);
       const uint4 wb = ld_u4(ba_w + (size_t)hv * a.k_in + e);
       const uint4 wa = ld_u4(ba_w + (size_t)(HV + hv) * a.k_in + e);
-      const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w}, bs[4] = {wb.x, wb.y, wb.z, wb.w}, as[4] = {wa.x, wa.y, wa.z, wa.w};
+      const uint32_t bs[4] = {wb.x, wb.y, wb.z, wb.w}, as[4] = {wa.x, wa.y, wa.z, wa.w};
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        sums[0] = fmaf(bf16_lo(xs[p]), bf16_lo(bs[p]), sums[0]);
-        sums[0] = fmaf(bf16_hi(xs[p]), bf16_hi(bs[p]), sums[0]);
-        sums[1] = fmaf(bf16_lo(xs[p]), bf16_lo(as[p]), sums[1]);
-        sums[1] = fmaf(bf16_hi(xs[p]), bf16_hi(as[p]), sums[1]);
+      for (int tt = 0; tt < kMaxTokens; ++tt) {
+        if (tt < nt) {
+          const uint4 xv = ld_u4(hidden + (size_t)(req * T + t0 + tt) * a.k_in + e);
+          const uint32_t xs[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            sums[4 * tt] = fmaf(bf16_lo(xs[p]), bf16_lo(bs[p]), sums[4 * tt]);
+            sums[4 * tt] = fmaf(bf16_hi(xs[p]), bf16_hi(bs[p]), sums[4 * tt]);
+            sums[4 * tt + 1] = fmaf(bf16_lo(xs[p]), bf16_lo(as[p]), sums[4 * tt + 1]);
+            sums[4 * tt + 1] = fmaf(bf16_hi(xs[p]), bf16_hi(as[p]), sums[4 * tt + 1]);
+          }
+        }
       }
     }
-    float qv = 0.f, kv = 0.f;
-    if (tid < kD) {
-      qv = __bfloat162float(mixed[(size_t)row * conv_dim + kh * kD + tid]);
-      kv = __bfloat162float(mixed[(size_t)row * conv_dim + (HK + kh) * kD + tid]);
-      sums[2] = qv * qv;
-      sums[3] = kv * kv;
-    } else {
-      const int d = tid - kD;
-      s_v[d] = __bfloat162float(mixed[(size_t)row * conv_dim + (2 * HK) * kD + hv * kD + d]);
-      s_z[d] = __bfloat162float(qkvz[(size_t)row * a.qkvz_stride + conv_dim + hv * kD + d]);
-    }
-    block_sum<4>(sums, s_red);
-    if (tid < kD) {
-      s_q[tid] = qv / sqrtf(sums[2] + 1e-6f) * a.scale;
-      s_k[tid] = kv / sqrtf(sums[3] + 1e-6f);
-    }
-    const float bb = round_bf16(sums[0]), aa = round_bf16(sums[1]);
-    const float x = aa + dt_bias;
-    const float softplus = x <= 20.0f ? log1pf(expf(x)) : x;
-    const float decay = expf(-expf(a_log) * softplus);
-    float beta = 1.0f / (1.0f + expf(-bb));
-    if (!verify) beta = round_bf16(beta);
-    __syncthreads();
-
-    // S <- S * decay;  v' = (v - S k) * beta;  S <- S + v' (x) k;  o = S q
-    float hk_part = 0.f;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float4 kk = *reinterpret_cast<const float4*>(&s_k[4 * (2 * j + half)]);
-      h[j].x *= decay;
-      h[j].y *= decay;
-      h[j].z *= decay;
-      h[j].w *= decay;
-      hk_part = fmaf(h[j].x, kk.x, hk_part);
-      hk_part = fmaf(h[j].y, kk.y, hk_part);
-      hk_part = fmaf(h[j].z, kk.z, hk_part);
-      hk_part = fmaf(h[j].w, kk.w, hk_part);
+    for (int tt = 0; tt < kMaxTokens; ++tt) {
+      qv[tt] = kv[tt] = 0.f;
+      if (tt < nt) {
+        const size_t row = (size_t)(req * T + t0 + tt);
+        if (tid < kD) {
+          qv[tt] = __bfloat162float(mixed[row * conv_dim + kh * kD + tid]);
+          kv[tt] = __bfloat162float(mixed[row * conv_dim + (HK + kh) * kD + tid]);
+          sums[4 * tt + 2] = qv[tt] * qv[tt];
+          sums[4 * tt + 3] = kv[tt] * kv[tt];
+        } else {
+          s_v[tt][tid - kD] = __bfloat162float(mixed[row * conv_dim + (2 * HK) * kD + hv * kD + tid - kD]);
+        }
+      }
     }
-    const float hk_full = hk_part + __shfl_xor_sync(0xffffffffu, hk_part, 1);
-    const float vn = (s_v[i] - hk_full) * beta;
-    float o_part = 0.f;
+    block_sum<4 * kMaxTokens>(sums, s_red);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float4 kk = *reinterpret_cast<const float4*>(&s_k[4 * (2 * j + half)]);
-      const float4 qq = *reinterpret_cast<const float4*>(&s_q[4 * (2 * j + half)]);
-      h[j].x = fmaf(vn, kk.x, h[j].x);
-      h[j].y = fmaf(vn, kk.y, h[j].y);
-      h[j].z = fmaf(vn, kk.z, h[j].z);
-      h[j].w = fmaf(vn, kk.w, h[j].w);
-      o_part = fmaf(h[j].x, qq.x, o_part);
-      o_part = fmaf(h[j].y, qq.y, o_part);
-      o_part = fmaf(h[j].z, qq.z, o_part);
-      o_part = fmaf(h[j].w, qq.w, o_part);
-    }
-    const float o_full = o_part + __shfl_xor_sync(0xffffffffu, o_part, 1);
-    if (half == 0) s_o[i] = round_bf16(o_full);
-    if (islot >= 0) {
-      float* snap = a.inter_ssm + ((((size_t)islot * T + t) * HV + hv) * kD + i) * kD;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) __stcs(reinterpret_cast<float4*>(snap + 4 * (2 * j + half)), h[j]);
+    for (int tt = 0; tt < kMaxTokens; ++tt) {
+      if (tt < nt) {
+        if (tid < kD) {
+          s_q[tt][tid] = qv[tt] / sqrtf(sums[4 * tt + 2] + 1e-6f) * a.scale;
+          s_k[tt][tid] = kv[tt] / sqrtf(sums[4 * tt + 3] + 1e-6f);
+        }
+        if (tid == 0) {
+          const float bb = round_bf16(sums[4 * tt]), aa = round_bf16(sums[4 * tt + 1]);
+          const float x = aa + dt_bias;
+          const float softplus = x <= 20.0f ? log1pf(expf(x)) : x;
+          s_decay[tt] = expf(-expf(a_log) * softplus);
+          const float beta = 1.0f / (1.0f + expf(-bb));
+          s_beta[tt] = verify ? beta : round_bf16(beta);
+        }
+      }
     }
     __syncthreads();
-
-    // gated RMSNorm over the head's 128 outputs, then the FP8 group of the next projection
-    const float o = tid < kD ? s_o[tid] : 0.f;
-    float ss[1] = {o * o};
-    block_sum<1>(ss, s_red);
-    const float rstd = rsqrtf(ss[0] / kD + a.eps);
-    float yf = 0.f;
-    if (tid < kD) {
-      const float z = s_z[tid];
-      const float y = o * rstd * nw * (z * (1.0f / (1.0f + expf(-z))));
-      yf = round_bf16(y);
-      out[(size_t)row * HV * kD + hv * kD + tid] = __float2bfloat16_rn(y);
+    // ---- phase B:  S <- S * decay;  v' = (v - S k) * beta;  S <- S + v' (x) k;  o = S q
+    for (int tt = 0; tt < nt; ++tt) {
+      const float decay = s_decay[tt], beta = s_beta[tt];
+      float hk_part = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float4 kk = *reinterpret_cast<const float4*>(&s_k[tt][4 * (2 * j + half)]);
+        h[j].x *= decay;
+        h[j].y *= decay;
+        h[j].z *= decay;
+        h[j].w *= decay;
+        hk_part = fmaf(h[j].x, kk.x, hk_part);
+        hk_part = fmaf(h[j].y, kk.y, hk_part);
+        hk_part = fmaf(h[j].z, kk.z, hk_part);
+        hk_part = fmaf(h[j].w, kk.w, hk_part);
+      }
+      const float hk_full = hk_part + __shfl_xor_sync(0xffffffffu, hk_part, 1);
+      const float vn = (s_v[tt][i] - hk_full) * beta;
+      float o_part = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float4 kk = *reinterpret_cast<const float4*>(&s_k[tt][4 * (2 * j + half)]);
+        const float4 qq = *reinterpret_cast<const float4*>(&s_q[tt][4 * (2 * j + half)]);
+        h[j].x = fmaf(vn, kk.x, h[j].x);
+        h[j].y = fmaf(vn, kk.y, h[j].y);
+        h[j].z = fmaf(vn, kk.z, h[j].z);
+        h[j].w = fmaf(vn, kk.w, h[j].w);
+        o_part = fmaf(h[j].x, qq.x, o_part);
+        o_part = fmaf(h[j].y, qq.y, o_part);
+        o_part = fmaf(h[j].z, qq.z, o_part);
+        o_part = fmaf(h[j].w, qq.w, o_part);
+      }
+      const float o_full = o_part + __shfl_xor_sync(0xffffffffu, o_part, 1);
+      if (half == 0) s_o[tt][i] = round_bf16(o_full);
+      if (islot >= 0) {
+        float* snap = a.inter_ssm + ((((size_t)islot * T + t0 + tt) * HV + hv) * kD + i) * kD;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) __stcs(reinterpret_cast<float4*>(snap + 4 * (2 * j + half)), h[j]);
+      }
     }
-    const float amax = block_max(fabsf(yf), s_red);
-    const float gs = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
-    const float inv = 1.0f / gs;
-    // four neighbours pack one 32-bit store
-    const float y1 = __shfl_down_sync(0xffffffffu, yf, 1), y2 = __shfl_down_sync(0xffffffffu, yf, 2),
-                y3 = __shfl_down_sync(0xffffffffu, yf, 3);
-    if (tid < kD && (tid & 3) == 0) {
-      auto q = [&](float y) { return fminf(fmaxf(y * inv, -448.f), 448.f); };
-      *reinterpret_cast<uint32_t*>(out_q + (size_t)row * HV * kD + hv * kD + tid) = f32x4_to_e4m3x4(q(yf), q(y1), q(y2), q(y3));
+    __syncthreads();
+    // ---- phase C: gated RMSNorm over the head's 128 outputs, then the FP8 group of the next projection
+    float ss[kMaxTokens], yf[kMaxTokens];
+#pragma unroll
+    for (int tt = 0; tt < kMaxTokens; ++tt) {
+      const float o = (tt < nt && tid < kD) ? s_o[tt][tid] : 0.f;
+      ss[tt] = o * o;
     }
-    if (tid == 0) a.out_scale[(size_t)row * HV + hv] = gs;
-    __syncthreads();  // s_q .. s_o are rewritten by the next token
+    block_sum<kMaxTokens>(ss, s_red);
+#pragma unroll
+    for (int tt = 0; tt < kMaxTokens; ++tt) {
+      yf[tt] = 0.f;
+      if (tt < nt && tid < kD) {
+        const size_t row = (size_t)(req * T + t0 + tt);
+        const float z = __bfloat162float(qkvz[row * a.qkvz_stride + conv_dim + hv * kD + tid]);
+        const float rstd = rsqrtf(ss[tt] / kD + a.eps);
+        const float y = s_o[tt][tid] * rstd * nw * (z * (1.0f / (1.0f + expf(-z))));
+        yf[tt] = round_bf16(y);
+        out[row * HV * kD + hv * kD + tid] = __float2bfloat16_rn(y);
+      }
+    }
+    // group maxima of all tokens: warps 0..3 hold the head's 128 values
+    __syncthreads();
+#pragma unroll
+    for (int tt = 0; tt < kMaxTokens; ++tt) {
+      const float m = warp_max(fabsf(yf[tt]));
+      if ((tid & 31) == 0) s_red[(tid >> 5) * kMaxTokens + tt] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int tt = 0; tt < kMaxTokens; ++tt) {
+      if (tt < nt) {
+        const size_t row = (size_t)(req * T + t0 + tt);
+        const float amax = fmaxf(fmaxf(s_red[tt], s_red[kMaxTokens + tt]), fmaxf(s_red[2 * kMaxTokens + tt], s_red[3 * kMaxTokens + tt]));
+        const float gs = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+        const float inv = 1.0f / gs;
+        // four neighbours pack one 32-bit store
+        const float y1 = __shfl_down_sync(0xffffffffu, yf[tt], 1), y2 = __shfl_down_sync(0xffffffffu, yf[tt], 2),
+                    y3 = __shfl_down_sync(0xffffffffu, yf[tt], 3);
+        if (tid < kD && (tid & 3) == 0) {
+          auto q = [&](float y) { return fminf(fmaxf(y * inv, -448.f), 448.f); };
+          *reinterpret_cast<uint32_t*>(out_q + row * HV * kD + hv * kD + tid) = f32x4_to_e4m3x4(q(yf[tt]), q(y1), q(y2), q(y3));
+        }
+        if (tid == 0) a.out_scale[row * HV + hv] = gs;
+      }
+    }
+    __syncthreads();  // shared arrays are rewritten by the next pass
   }
   if (!verify) {
 #pragma unroll

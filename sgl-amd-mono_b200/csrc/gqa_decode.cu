@@ -58,19 +58,27 @@ __global__ __launch_bounds__(128) void gqa_split_kernel(B200GqaArgs a) {
       val = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q) + ((size_t)t * a.q_heads + kvh * G + h) * D)[v];
     *reinterpret_cast<uint4*>(&sm.q[h][v * 8]) = val;
   }
-  // K and V rows of the chunk
-  for (int i = threadIdx.x; i < kGqaChunk * VPR; i += 128) {
-    const int key = i / VPR, v = i % VPR;
-    uint4 kk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-    if (key < n_here) {
-      const int pos = key0 + key;
-      const size_t slot = (size_t)pages[pos >> 6] * 64 + (pos & 63);
-      const size_t off = (slot * a.kv_heads + kvh) * D;
-      kk = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.k_cache) + off)[v];
-      vv = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.v_cache) + off)[v];
+  // K and V rows of the chunk: exactly two 64-token pages, resolved once; every 16-byte piece is an asynchronous
+  // copy straight into shared memory (zero-filled past the row's last key), all in flight together
+  {
+    const int page0 = pages[2 * chunk], page1 = n_here > 64 ? pages[2 * chunk + 1] : 0;
+    const size_t row_elems = (size_t)a.kv_heads * D;
+    const __nv_bfloat16* kc = reinterpret_cast<const __nv_bfloat16*>(a.k_cache) + (size_t)kvh * D;
+    const __nv_bfloat16* vc = reinterpret_cast<const __nv_bfloat16*>(a.v_cache) + (size_t)kvh * D;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < kGqaChunk * VPR; i += 128) {
+      const int key = i / VPR, v = i % VPR;
+      const size_t slot = (size_t)(key < 64 ? page0 : page1) * 64 + (key & 63);
+      const uint32_t bytes = key < n_here ? 16u : 0u;
+      const size_t off = slot * row_elems + (size_t)v * 8;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(&sm.k[key][v * 8])),
+                   "l"(kc + off), "r"(bytes)
+                   : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(&sm.v[key][v * 8])),
+                   "l"(vc + off), "r"(bytes)
+                   : "memory");
     }
-    *reinterpret_cast<uint4*>(&sm.k[key][v * 8]) = kk;
-    *reinterpret_cast<uint4*>(&sm.v[key][v * 8]) = vv;
+    asm volatile("cp.async.wait_all;" ::: "memory");
   }
   __syncthreads();
 
@@ -162,23 +170,60 @@ __global__ __launch_bounds__(128) void gqa_split_kernel(B200GqaArgs a) {
   }
 }
 
-// grid (q_heads, rows), D threads
-__global__ void gqa_combine_kernel(B200GqaArgs a) {
+// grid (q_heads, rows), block (D, 1024 / D): thread (d, slice) merges the chunks slice, slice + S, ... of dim d, eight
+// loads in flight at a time; the slices meet in shared memory.  Chunk weights w_c = exp(m_c - M) are computed once
+// by the whole block.
+constexpr int kCombineChunks = 1024;  // chunks whose weights fit the shared array (131072 keys)
+__global__ __launch_bounds__(1024) void gqa_combine_kernel(B200GqaArgs a) {
   pdl_enter();
-  const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x, D = a.head_dim;
+  __shared__ float s_w[kCombineChunks];
+  __shared__ float s_redm[32], s_redl[32];
+  __shared__ float s_acc[8][256];
+  const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x, slice = threadIdx.y, D = a.head_dim;
+  const int S = blockDim.y, tid = slice * D + d, nthreads = D * S;
   const int nch = (a.ctx_len[t] + kGqaChunk - 1) / kGqaChunk;
+  const int ch0 = a.window > 0 ? max(0, a.ctx_len[t] - a.window) / kGqaChunk : 0;
   const float* ml = a.part_ml + (((size_t)t * a.q_heads + h) * a.max_chunks) * 2;
   const float* po = a.part_o + (((size_t)t * a.q_heads + h) * a.max_chunks) * D;
-  const int ch0 = a.window > 0 ? max(0, a.ctx_len[t] - a.window) / kGqaChunk : 0;
+  // M = max m_c
+  float m = -INFINITY;
+  for (int ch = ch0 + tid; ch < nch; ch += nthreads) m = fmaxf(m, ml[2 * ch]);
+  m = warp_max(m);
+  if ((tid & 31) == 0) s_redm[tid >> 5] = m;
+  __syncthreads();
   float M = -INFINITY;
-  for (int ch = ch0; ch < nch; ++ch) M = fmaxf(M, ml[2 * ch]);
-  float den = 0.f, acc = 0.f;
-  for (int ch = ch0; ch < nch; ++ch) {
+  for (int w = 0; w < nthreads / 32; ++w) M = fmaxf(M, s_redm[w]);
+  // weights and the denominator (warp partials added in warp order)
+  float l = 0.f;
+  for (int ch = ch0 + tid; ch < nch; ch += nthreads) {
     const float w = __expf(ml[2 * ch] - M);
-    den += ml[2 * ch + 1] * w;
-    acc += po[(size_t)ch * D + d] * w;
+    if (ch - ch0 < kCombineChunks) s_w[ch - ch0] = w;
+    l += ml[2 * ch + 1] * w;
   }
-  reinterpret_cast<__nv_bfloat16*>(a.out)[((size_t)t * a.q_heads + h) * D + d] = __float2bfloat16_rn(den > 0.f ? acc / den : 0.f);
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+  if ((tid & 31) == 0) s_redl[tid >> 5] = l;
+  __syncthreads();
+  float den = 0.f;
+  for (int w = 0; w < nthreads / 32; ++w) den += s_redl[w];
+  float acc = 0.f;
+  for (int c0 = ch0 + slice; c0 < nch; c0 += 8 * S) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = c0 + u * S < nch ? __ldcs(po + (size_t)(c0 + u * S) * D + d) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int ch = c0 + u * S;
+      if (ch < nch) acc += v[u] * (ch - ch0 < kCombineChunks ? s_w[ch - ch0] : __expf(ml[2 * ch] - M));
+    }
+  }
+  s_acc[slice][d] = acc;
+  __syncthreads();
+  if (slice == 0) {
+    float tot = 0.f;
+    for (int sl = 0; sl < S; ++sl) tot += s_acc[sl][d];
+    reinterpret_cast<__nv_bfloat16*>(a.out)[((size_t)t * a.q_heads + h) * D + d] = __float2bfloat16_rn(den > 0.f ? tot / den : 0.f);
+  }
 }
 
 // new tokens' K and V rows into their cache slots (pad rows, slot <= 0, write nothing): grid rows, 128 threads
@@ -211,8 +256,8 @@ static cudaError_t launch_gqa_d(const B200GqaArgs& a, cudaStream_t s) {
   launch_pdl(gqa_split_kernel<D>, grid, 128, sizeof(GqaSmem<D>), s, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  dim3 grid2(a.q_heads, a.rows);
-  launch_pdl(gqa_combine_kernel, grid2, D, 0, s, a);
+  dim3 grid2(a.q_heads, a.rows), block2(D, 1024 / D);
+  launch_pdl(gqa_combine_kernel, grid2, block2, 0, s, a);
   return cudaGetLastError();
 }
 

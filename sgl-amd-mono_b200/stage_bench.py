@@ -1,0 +1,159 @@
+"""Times single stages alone on one GPU (the counterpart of the reference's kernel timers,
+test/kernels/glm53/time_layers.py): seeded synthetic inputs, L2 flushed before every timed launch, CUDA events on
+the launching stream, median of `--reps`.  Prints one JSON line per stage with its algorithmic bytes and GB/s.
+
+    python sgl-amd-mono_b200/stage_bench.py [--stages gqa,gdn,index,topk] [--reps 20]
+
+Stages: gqa (dense GQA decode: 8 rows, contexts uniform in [1024, 32768), 8 query heads on 1 KV head, d = 128, and
+16 on 2 with d = 256 at context 8192), gdn (verify chain: 8 requests x 4 tokens, 16 key / 32 value heads; decode:
+8 requests), index (index scores, 8 rows, contexts in [4096, 65536), both kernels), topk (exact top-2048 of them).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import sgl_amd_mono_b200  # noqa: E402,F401
+from sgl_amd_mono_b200 import cabi  # noqa: E402
+
+DEV = "cuda:0"
+
+
+def timed(fn, reps, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def report(stage, us, nbytes, **extra):
+    print(json.dumps(dict(stage=stage, us=round(us, 2), algorithmic_bytes=int(nbytes), gbs=round(nbytes / us / 1e3, 1), **extra)))
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def bench_gqa(lib, reps, flush):
+    g = torch.Generator().manual_seed(3)
+    for name, rows, hq, hkv, d, lo, hi in [("gqa d128 8q/1kv ctx U[1024,32768)", 8, 8, 1, 128, 1024, 32768),
+                                           ("gqa d256 16q/2kv ctx 8192", 8, 16, 2, 256, 8192, 8193)]:
+        ctx = torch.randint(lo, hi, (rows,), generator=g)
+        max_pages = (int(ctx.max()) + 63) // 64
+        max_pages += max_pages & 1
+        n_pages = rows * max_pages + 1
+        kc = torch.randn(n_pages * 64, hkv, d, device=DEV).bfloat16()
+        vc = torch.randn(n_pages * 64, hkv, d, device=DEV).bfloat16()
+        table = (torch.randperm(n_pages - 1, generator=g)[: rows * max_pages] + 1).view(rows, max_pages).to(torch.int32).to(DEV)
+        q = torch.randn(rows, hq, d, device=DEV).bfloat16()
+        chunks = (int(ctx.max()) + 127) // 128
+        part_o = torch.empty(rows, hq, chunks, d, device=DEV)
+        part_ml = torch.empty(rows, hq, chunks, 2, device=DEV)
+        out = torch.empty(rows, hq, d, dtype=torch.bfloat16, device=DEV)
+        req = torch.arange(rows, dtype=torch.int32, device=DEV)
+        cl = ctx.to(torch.int32).to(DEV)
+        a = cabi.fill("B200GqaArgs", q=q, k_cache=kc, v_cache=vc, page_table=table, req_of_row=req, ctx_len=cl, part_o=part_o,
+                      part_ml=part_ml, out=out, rows=rows, q_heads=hq, kv_heads=hkv, head_dim=d, max_pages=max_pages,
+                      max_chunks=chunks, window=0, scale=d ** -0.5)
+        us = timed(lambda: lib.call("gqa_decode", a, stream()), reps, flush)
+        report(name, us, int(ctx.sum()) * 2 * hkv * d * 2, rows=rows)
+
+
+def bench_gdn(lib, reps, flush):
+    g = torch.Generator().manual_seed(5)
+    hk, hv, k_in, D = 16, 32, 2048, 128
+    conv_dim = (2 * hk + hv) * D
+    for name, R, T, commit in [("gdn verify 8 requests x 4 tokens", 8, 4, 0), ("gdn decode 8 requests", 8, 1, 1)]:
+        rows = R * T
+        d = lambda *s, dt=torch.bfloat16, sc=1.0: (torch.randn(*s, generator=g) * sc).to(dt).to(DEV)
+        qkvz, hidden = d(rows, conv_dim + hv * D), d(rows, k_in)
+        ba_w, conv_w, norm_w = d(2 * hv, k_in, sc=0.05), d(conv_dim, 4, sc=0.5), d(D)
+        a_log, dt_bias = d(hv, dt=torch.float32, sc=0.5), d(hv, dt=torch.float32)
+        conv_state = d(R + 1, 3, conv_dim)
+        ssm = d(R + 1, hv, D, D, dt=torch.float32, sc=0.1)
+        inter_conv = torch.zeros(R, T, 3, conv_dim, dtype=torch.bfloat16, device=DEV)
+        inter_ssm = torch.zeros(R, T, hv, D, D, device=DEV)
+        slot = (torch.randperm(R + 1, generator=g)[:R]).to(torch.int32).to(DEV)
+        islot = torch.randperm(R, generator=g).to(torch.int32).to(DEV)
+        mixed = torch.empty(rows, conv_dim, dtype=torch.bfloat16, device=DEV)
+        out = torch.empty(rows, hv * D, dtype=torch.bfloat16, device=DEV)
+        out_q = torch.empty(rows, hv * D, dtype=torch.uint8, device=DEV)
+        out_s = torch.empty(rows, hv, device=DEV)
+        a = cabi.fill("B200GdnArgs", qkvz=qkvz, hidden=hidden, ba_w=ba_w, conv_w=conv_w, conv_state=conv_state, ssm_state=ssm,
+                      slot=slot, inter_slot=islot, inter_conv=inter_conv, inter_ssm=inter_ssm, a_log=a_log, dt_bias=dt_bias,
+                      norm_w=norm_w, mixed=mixed, out=out, out_q=out_q, out_scale=out_s, requests=R, tokens=T, hk=hk, hv=hv,
+                      k_in=k_in, qkvz_stride=qkvz.shape[1], commit=commit, scale=D ** -0.5, eps=1e-6)
+        us = timed(lambda: lib.call("gdn", a, stream()), reps, flush)
+        state = R * hv * D * D * 4
+        report(name, us, state * (1 + T if not commit else 2), state_read=state, state_written=state * (T if not commit else 1))
+
+
+def _index_inputs(rows=8):
+    g = torch.Generator().manual_seed(0)
+    ctx = torch.randint(4096, 65536, (rows,), generator=g)
+    max_pages = (int(ctx.max()) + 63) // 64
+    n_pages = rows * max_pages + 1
+    q_rec = torch.randint(0, 256, (rows, 64, 68), generator=g, dtype=torch.uint8)
+    q_rec[:, :, 64:] = torch.randint(118, 131, (rows, 64, 4), generator=g, dtype=torch.uint8)
+    w = torch.randn(rows, 64, generator=g) * 0.1
+    cache = torch.randint(0, 256, (n_pages, 4352), generator=g, dtype=torch.uint8)
+    cache[:, 4096:] = torch.randint(118, 131, (n_pages, 256), generator=g, dtype=torch.uint8)
+    table = (torch.randperm(n_pages - 1, generator=g)[: rows * max_pages] + 1).view(rows, max_pages).to(torch.int32)
+    t = dict(q_rec=q_rec.to(DEV), w=w.to(DEV), idx_cache=cache.to(DEV), page_table=table.to(DEV),
+             req_of_row=torch.arange(rows, dtype=torch.int32, device=DEV), ctx_len=ctx.to(torch.int32).to(DEV))
+    return t, ctx, max_pages
+
+
+def bench_index(lib, reps, flush, with_topk):
+    t, ctx, max_pages = _index_inputs()
+    rows, stride = len(ctx), max_pages * 64
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scores = torch.zeros(rows, stride, device=DEV)
+    for variant, name in [(0, "index scores, tcgen05"), (1, "index scores, mma.sync")]:
+        a = cabi.fill("B200IndexScoreArgs", scores=scores, rows=rows, max_pages=max_pages, max_ctx=int(ctx.max()),
+                      score_stride=stride, status=status, variant=variant, **t)
+        us = timed(lambda: lib.call("index_score", a, stream()), reps, flush)
+        report(name, us, int(ctx.sum()) * 68, rows=rows, keys=int(ctx.sum()), status=int(status))
+    if with_topk:
+        idx = torch.zeros(rows, 2048, dtype=torch.int32, device=DEV)
+        cnt = torch.zeros(rows, dtype=torch.int32, device=DEV)
+        a = cabi.fill("B200TopkArgs", scores=scores, ctx_len=t["ctx_len"], topk_idx=idx, topk_count=cnt, rows=rows, k=2048,
+                      score_stride=stride)
+        us = timed(lambda: lib.call("topk", a, stream()), reps, flush)
+        report("exact top-2048", us, int(ctx.sum()) * 4, rows=rows)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--stages", default="gqa,gdn,index,topk")
+    ap.add_argument("--reps", type=int, default=20)
+    args = ap.parse_args()
+    lib = cabi.lib()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    stages = set(args.stages.split(","))
+    if "gqa" in stages:
+        bench_gqa(lib, args.reps, flush)
+    if "gdn" in stages:
+        bench_gdn(lib, args.reps, flush)
+    if "index" in stages or "topk" in stages:
+        bench_index(lib, args.reps, flush, "topk" in stages)
+
+
+if __name__ == "__main__":
+    main()
