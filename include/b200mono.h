@@ -470,6 +470,43 @@ typedef struct {
 } B200QuantMxfp8Args;
 int b200mono_quant_mxfp8(const B200QuantMxfp8Args* a, void* stream);
 
+/* Experts with MXFP4 weights on MXFP8 rows (configs with e2m1 + e8m0/32 expert weights): gate/up + SwiGLU, and down +
+ * slot-ordered combine.  Replace gemv_fp4_pair / ug_pass / ug_epilogue / stage_down / down_combine
+ * (sgl_amd_mono/deepseek_v41/gfx950/stages/moe.py:393-1227) and glm53 sections 9-10
+ * (sgl_amd_mono/glm53/gfx950/kernel.py:5662-7150); torch: test/kernels/glm53/check_mxfp4.py:40-78.
+ * Weights are in this library's tile packing (made once at load time by sgl-amd-mono_b200/mx4.py::pack_mxfp4, the
+ * counterpart of the reference's shuffle_weight / e8m0_shuffle): codes [N/16][K/64][32][16] bytes, scales
+ * [N/16][K/64][8][4] bytes, N = all experts' rows stacked (shared expert last).  Activations: b200mono_quant_mxfp8.
+ * Up to 8 rows per launch. */
+typedef struct {
+  const void* w13;             /* packed codes of [E+1][2*inter][hidden] (gate rows then up rows per expert) */
+  const void* w13_scale;       /* packed scales */
+  const void* xq;              /* e4m3 [rows, hidden] */
+  const void* x_scale;         /* u8 [rows, hidden/32] */
+  const int32_t* union_ids;    /* int32 [union_cap]: picked experts (shared = experts) */
+  const int32_t* union_count;
+  void* mid;                   /* bf16 [union_cap][rows][inter] out */
+  int32_t rows, hidden, inter, experts, union_cap;
+  float swiglu_limit;          /* > 0: silu(min(g, L)) * clamp(u, +-L) */
+} B200Mx4UpArgs;
+int b200mono_mx4_up(const B200Mx4UpArgs* a, void* stream);
+
+typedef struct {
+  const void* w2;              /* packed codes of [E+1][hidden][inter] */
+  const void* w2_scale;
+  const void* midq;            /* e4m3 [union_cap][rows][inter] */
+  const void* mid_scale;       /* u8 [union_cap][rows][inter/32] */
+  const int32_t* union_ids;
+  const int32_t* union_count;
+  const uint8_t* union_pick;   /* u8 [union_cap][32]: 0 or (slot of the row's top-k) + 1 */
+  const float* topk_w;         /* f32 [rows, topk] */
+  void* contrib;               /* bf16 [topk + has_shared][rows][hidden] scratch */
+  const void* residual;        /* bf16 [rows, hidden] or NULL */
+  void* out;                   /* bf16 [rows, hidden] */
+  int32_t rows, hidden, inter, experts, topk, has_shared, union_cap, pad_;
+} B200Mx4DownArgs;
+int b200mono_mx4_down(const B200Mx4DownArgs* a, void* stream);
+
 /* ------------------------------------------------------------------------
  * The same block for callers that cannot allocate device memory.  This entry
  * point has no counterpart in the reference (its runner always owns a scratch

@@ -184,3 +184,50 @@ def moe_ffn(x, w, cfg, residual=None, add_residual=False, route_from=None):
         acc = Q.bf(acc + s.float())
     return dict(s=s, xn=xn, xq=xq, xs=xs, logits=logits, ids=ids, wts=wts, union=uni, pick=pick,
                 mids=mids, out=acc.to(torch.bfloat16))
+
+
+def expert_mid_mx4(xq, xc, w13_codes, w13_sc, limit: float) -> torch.Tensor:
+    """bf16 SwiGLU output of one MXFP4 expert on MXFP8 rows (test/kernels/glm53/check_mxfp4.py:66-78): both operands
+    dequantised exactly, f64 accumulation."""
+    inter = w13_codes.shape[0] // 2
+    h = (Q.mxfp8_dequant(xq, xc).double() @ Q.dequantize_mxfp4(w13_codes, w13_sc).double().T).float()
+    g, u = h[:, :inter], h[:, inter:]
+    if limit > 0:
+        g = g.clamp(max=limit)
+        u = u.clamp(-limit, limit)
+    return (torch.nn.functional.silu(g) * u).to(torch.bfloat16)
+
+
+def moe_ffn_mx4(x, w, cfg, residual=None, add_residual=False, route_from=None, rule="aiter"):
+    """The MoE FFN block with MXFP4 expert weights on MXFP8 rows; same structure and slot-ordered bf16 sum as moe_ffn.
+    w: norm, gate_w, bias|None, w13_codes u8 [E+1, 2I, H/2], w13_sc u8 [E+1, 2I, H/32], w2_codes u8 [E+1, H, I/2],
+    w2_sc u8 [E+1, H, I/32]."""
+    rows, hidden = x.shape
+    E, k = cfg["experts"], cfg["topk"]
+    x = x.cpu()
+    residual = None if residual is None else residual.cpu()
+    s, xn, _, _ = rmsnorm_quant(x, w["norm"], cfg["eps"], residual)
+    xq, xc = Q.mxfp8_quant(xn, rule)
+    logits = router_logits(xn if route_from is None else route_from, w["gate_w"])
+    bias = None if w.get("bias") is None else _np(w["bias"])
+    ids, wts = route(logits, bias, k, cfg["score_fn"], cfg.get("route_scale", 1.0))
+    uni, pick = union_of(ids, E, cfg["has_shared"])
+    mids = {}
+    per_slot = torch.zeros(k + 1, rows, hidden)
+    for u, e in enumerate(uni.tolist()):
+        mid = expert_mid_mx4(xq, xc, w["w13_codes"][e], w["w13_sc"][e], cfg.get("swiglu_limit", 0.0))
+        mids[e] = mid
+        mq, mc = Q.mxfp8_quant(mid, rule)
+        y = (Q.mxfp8_dequant(mq, mc).double() @ Q.dequantize_mxfp4(w["w2_codes"][e], w["w2_sc"][e]).double().T).float()
+        for t in range(rows):
+            sl = int(pick[u, t])
+            if sl:
+                wgt = float(wts[t, sl - 1]) if sl <= k else 1.0
+                per_slot[sl - 1, t] = Q.bf(y[t] * np.float32(wgt))
+    acc = torch.zeros(rows, hidden)
+    for sl in range(k + (1 if cfg["has_shared"] else 0)):
+        acc = Q.bf(acc + per_slot[sl])
+    if add_residual:
+        acc = Q.bf(acc + s.float())
+    return dict(s=s, xn=xn, xq=xq, xc=xc, logits=logits, ids=ids, wts=wts, union=uni, pick=pick, mids=mids,
+                out=acc.to(torch.bfloat16))

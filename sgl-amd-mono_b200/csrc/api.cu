@@ -64,7 +64,8 @@ int b200mono_abi_sizes(int32_t* out, int32_t capacity) {
                            (int32_t)sizeof(B200IdxQPostArgs),  (int32_t)sizeof(B200IndexScoreArgs),
                            (int32_t)sizeof(B200TopkArgs),      (int32_t)sizeof(B200SparseMlaArgs),
                            (int32_t)sizeof(B200GqaArgs),      (int32_t)sizeof(B200GdnArgs),
-                           (int32_t)sizeof(B200QuantMxfp8Args)};
+                           (int32_t)sizeof(B200QuantMxfp8Args), (int32_t)sizeof(B200Mx4UpArgs),
+                           (int32_t)sizeof(B200Mx4DownArgs)};
   const int32_t n = (int32_t)(sizeof(sizes) / sizeof(sizes[0]));
   for (int32_t i = 0; i < n && i < capacity; ++i) out[i] = sizes[i];
   return n;
@@ -263,6 +264,30 @@ int b200mono_quant_mxfp8(const B200QuantMxfp8Args* a, void* stream) {
           "quant_mxfp8: rows=%d cols=%d (a multiple of 32) rule=%d", a->rows, a->cols, a->rule);
   REQUIRE(aligned(a->x, 16) && aligned(a->q, 8), "quant_mxfp8: x 16-byte, q 8-byte aligned");
   return cuda_status(launch_quant_mxfp8(*a, (cudaStream_t)stream), "quant_mxfp8");
+}
+
+int b200mono_mx4_up(const B200Mx4UpArgs* a, void* stream) {
+  REQUIRE(a && a->w13 && a->w13_scale && a->xq && a->x_scale && a->union_ids && a->union_count && a->mid, "mx4_up: null pointer");
+  REQUIRE(a->rows >= 1 && a->rows <= 8 && a->hidden >= 64 && a->hidden % 64 == 0 && a->inter >= 16 && a->inter % 16 == 0 &&
+              a->experts >= 1 && a->union_cap >= 1,
+          "mx4_up: rows=%d (1..8) hidden=%d (a multiple of 64) inter=%d (a multiple of 16) union_cap=%d", a->rows, a->hidden,
+          a->inter, a->union_cap);
+  REQUIRE(aligned(a->w13, 16) && aligned(a->w13_scale, 4) && aligned(a->xq, 8), "mx4_up: w13 16-byte, scales 4-byte, xq 8-byte aligned");
+  return cuda_status(launch_mx4_up(*a, (cudaStream_t)stream), "mx4_up");
+}
+
+int b200mono_mx4_down(const B200Mx4DownArgs* a, void* stream) {
+  REQUIRE(a && a->w2 && a->w2_scale && a->midq && a->mid_scale && a->union_ids && a->union_count && a->union_pick &&
+              a->topk_w && a->contrib && a->out,
+          "mx4_down: null pointer");
+  REQUIRE(a->rows >= 1 && a->rows <= 8 && a->hidden >= 16 && a->hidden % 16 == 0 && a->inter >= 64 && a->inter % 64 == 0 &&
+              a->topk >= 1 && a->topk <= 16 && a->union_cap >= 1,
+          "mx4_down: rows=%d (1..8) hidden=%d (a multiple of 16) inter=%d (a multiple of 64) topk=%d", a->rows, a->hidden,
+          a->inter, a->topk);
+  REQUIRE(aligned(a->w2, 16) && aligned(a->w2_scale, 4) && aligned(a->midq, 8) && aligned(a->contrib, 16) && aligned(a->out, 16) &&
+              (!a->residual || aligned(a->residual, 16)),
+          "mx4_down: w2, contrib, out, residual 16-byte, scales 4-byte, midq 8-byte aligned");
+  return cuda_status(launch_mx4_down(*a, (cudaStream_t)stream), "mx4_down");
 }
 
 int b200mono_gdn(const B200GdnArgs* a, void* stream) {

@@ -33,6 +33,11 @@ cudaError_t launch_topk(const B200TopkArgs& a, cudaStream_t s);
 cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s);
 cudaError_t launch_gqa(const B200GqaArgs& a, cudaStream_t s);
 cudaError_t launch_quant_mxfp8(const B200QuantMxfp8Args& a, cudaStream_t s);
+// slot-ordered bf16 sum of contrib [slots][rows][hidden] (+ residual) -> out
+cudaError_t launch_moe_combine(const void* contrib, const void* residual, void* out, int rows, int hidden, int slots,
+                               cudaStream_t s);
+cudaError_t launch_mx4_up(const B200Mx4UpArgs& a, cudaStream_t s);
+cudaError_t launch_mx4_down(const B200Mx4DownArgs& a, cudaStream_t s);
 cudaError_t launch_gdn(const B200GdnArgs& a, cudaStream_t s);
 cudaError_t launch_allreduce(const B200AllReduceArgs& a, cudaStream_t s);
 

@@ -1,0 +1,173 @@
+// Routed + shared experts with MXFP4 weights (E2M1 codes, one E8M0 scale per 32) on MXFP8 activation rows (e4m3, one
+// E8M0 scale per 32): y[t, n] = sum_G 2^(ws[n,G] + xs[t,G] - 254) * sum_{d in G} w[n,d] x[t,d].
+//
+// A 32-wide scale group is exactly one m16n8k32 e4m3 MMA step: every E2M1 value is exact in e4m3, so the codes are
+// expanded with one byte permute per four values and the two power-of-two scales are applied on the accumulator.
+// Weight rows are the MMA M dimension (tiles of 16), activation rows the N dimension (up to 8 per launch).
+//
+// Weights are read in a tile-major packing made once at load time (mx4.py, the counterpart of the reference's
+// shuffle_weight): [N/16][K/64][32 lanes][16 B], lane (g, c) holding, for the two scale groups of the 64-wide k unit,
+// the eight codes 8c..8c+7 of rows g and g+8, so that a warp reads one coalesced 512-byte line per k unit and every
+// lane's bytes are its MMA fragments.  Scales: [N/16][K/64][8 g][4 B] = (G0, g), (G0, g+8), (G1, g), (G1, g+8).
+#include "common.cuh"
+#include "launch.h"
+
+namespace b200mono {
+
+namespace {
+
+__device__ __forceinline__ uint32_t mx_e2m1x4_to_e4m3x4(uint32_t codes) {
+  const uint32_t lut_lo = 0x3c383000u, lut_hi = 0x4c484440u;  // 0, .5, 1, 1.5 | 2, 3, 4, 6 as e4m3
+  const uint32_t mag = __byte_perm(lut_lo, lut_hi, codes & 0x7777u);
+  const uint32_t s = codes & 0x8888u;
+  const uint32_t sign = ((s & 0x8u) << 4) | ((s & 0x80u) << 8) | ((s & 0x800u) << 12) | ((s & 0x8000u) << 16);
+  return mag | sign;
+}
+__device__ __forceinline__ float mx_e8m0(uint32_t code) {
+  return code == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(code << 23);
+}
+
+// One k unit (two scale groups) of one 16-row weight tile against 8 activation rows.
+//   wv: the lane's 16 packed bytes; wsc: the tile's scale word of row pair g; xrow: the lane's activation row (g),
+//   already offset to the unit's first dim + 8c (nullptr: row absent); xs0 / xs1: activation scales of columns 2c, 2c+1.
+__device__ __forceinline__ void mx_unit(float (&acc)[4], const uint4 wv, const uint32_t wsc, const uint8_t* xrow,
+                                        const float (&xs0)[2], const float (&xs1)[2]) {
+  const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+  for (int G = 0; G < 2; ++G) {
+    uint32_t b0 = 0, b1 = 0;
+    if (xrow) {
+      const uint2 xv = *reinterpret_cast<const uint2*>(xrow + 32 * G);
+      b0 = xv.x;
+      b1 = xv.y;
+    }
+    const uint32_t lo = w[2 * G], hi = w[2 * G + 1];  // row g, row g + 8
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+    mma_e4m3_16x8x32(d, mx_e2m1x4_to_e4m3x4(lo & 0xffffu), mx_e2m1x4_to_e4m3x4(hi & 0xffffu), mx_e2m1x4_to_e4m3x4(lo >> 16),
+                     mx_e2m1x4_to_e4m3x4(hi >> 16), b0, b1);
+    const float wa = mx_e8m0((wsc >> (16 * G)) & 0xffu), wb = mx_e8m0((wsc >> (16 * G + 8)) & 0xffu);
+    acc[0] = fmaf(d[0], wa * xs0[G], acc[0]);
+    acc[1] = fmaf(d[1], wa * xs1[G], acc[1]);
+    acc[2] = fmaf(d[2], wb * xs0[G], acc[2]);
+    acc[3] = fmaf(d[3], wb * xs1[G], acc[3]);
+  }
+}
+
+}  // namespace
+
+// grid (inter / 16, union slots): gate tile j and up tile j of one picked expert; the CTA's 8 warps split the k units.
+__global__ __launch_bounds__(256) void mx4_up_kernel(B200Mx4UpArgs a) {
+  pdl_enter();
+  __shared__ float s_red[8][2][4][32];
+  const int j = blockIdx.x, u = blockIdx.y;
+  if (u >= *a.union_count) return;
+  const int e = a.union_ids[u];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int units = a.hidden >> 6, T = a.rows;
+  const size_t tile_g = ((size_t)e * 2 * a.inter + (size_t)j * 16) >> 4, tile_u = tile_g + (a.inter >> 4);
+  const uint4* wg = reinterpret_cast<const uint4*>(a.w13) + tile_g * units * 32 + lane;
+  const uint4* wu = reinterpret_cast<const uint4*>(a.w13) + tile_u * units * 32 + lane;
+  const uint32_t* sg = reinterpret_cast<const uint32_t*>(a.w13_scale) + tile_g * units * 8 + g;
+  const uint32_t* su = reinterpret_cast<const uint32_t*>(a.w13_scale) + tile_u * units * 8 + g;
+  const uint8_t* xq = reinterpret_cast<const uint8_t*>(a.xq);
+  const uint8_t* xsc = reinterpret_cast<const uint8_t*>(a.x_scale);
+  const int ng = a.hidden >> 5;  // scale groups per activation row
+  float accg[4] = {0.f, 0.f, 0.f, 0.f}, accu[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int q = warp; q < units; q += 8) {
+    const uint4 vg = ld_stream_u4(wg + (size_t)q * 32), vu = ld_stream_u4(wu + (size_t)q * 32);
+    const uint32_t cg = __ldg(sg + (size_t)q * 8), cu = __ldg(su + (size_t)q * 8);
+    float xs0[2], xs1[2];
+#pragma unroll
+    for (int G = 0; G < 2; ++G) {
+      xs0[G] = 2 * c < T ? mx_e8m0(xsc[(size_t)(2 * c) * ng + 2 * q + G]) : 0.f;
+      xs1[G] = 2 * c + 1 < T ? mx_e8m0(xsc[(size_t)(2 * c + 1) * ng + 2 * q + G]) : 0.f;
+    }
+    const uint8_t* xrow = g < T ? xq + (size_t)g * a.hidden + 64 * q + 8 * c : nullptr;
+    mx_unit(accg, vg, cg, xrow, xs0, xs1);
+    mx_unit(accu, vu, cu, xrow, xs0, xs1);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    s_red[warp][0][i][lane] = accg[i];
+    s_red[warp][1][i][lane] = accu[i];
+  }
+  __syncthreads();
+  if (warp == 0) {
+    __nv_bfloat16* mid = reinterpret_cast<__nv_bfloat16*>(a.mid) + (size_t)u * a.rows * a.inter;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float gsum = 0.f, usum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {  // warp order
+        gsum += s_red[w][0][i][lane];
+        usum += s_red[w][1][i][lane];
+      }
+      const int row = g + ((i & 2) ? 8 : 0), t = 2 * c + (i & 1);
+      if (t < T) {
+        if (a.swiglu_limit > 0.f) {
+          gsum = fminf(gsum, a.swiglu_limit);
+          usum = fminf(fmaxf(usum, -a.swiglu_limit), a.swiglu_limit);
+        }
+        const float act = gsum / (1.0f + expf(-gsum));
+        mid[(size_t)t * a.inter + j * 16 + row] = __float2bfloat16_rn(act * usum);
+      }
+    }
+  }
+}
+
+// grid (hidden / 16, ceil(union slots / 8)): warp w takes union slot 8 * blockIdx.y + w and the CTA's 16 output rows;
+// the product goes, scaled by the routing weight, to contrib[slot of the row's top-k][row][column].
+__global__ __launch_bounds__(256) void mx4_down_kernel(B200Mx4DownArgs a) {
+  pdl_enter();
+  const int tile = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+  const int u = blockIdx.y * 8 + warp;
+  if (u >= *a.union_count) return;
+  const int e = a.union_ids[u];
+  const int units = a.inter >> 6, T = a.rows, ng = a.inter >> 5;
+  const size_t wt = ((size_t)e * a.hidden >> 4) + tile;
+  const uint4* w2 = reinterpret_cast<const uint4*>(a.w2) + wt * units * 32 + lane;
+  const uint32_t* s2 = reinterpret_cast<const uint32_t*>(a.w2_scale) + wt * units * 8 + g;
+  const uint8_t* xq = reinterpret_cast<const uint8_t*>(a.midq) + (size_t)u * T * a.inter;
+  const uint8_t* xsc = reinterpret_cast<const uint8_t*>(a.mid_scale) + (size_t)u * T * ng;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int q = 0; q < units; ++q) {
+    const uint4 wv = ld_stream_u4(w2 + (size_t)q * 32);
+    const uint32_t wsc = __ldg(s2 + (size_t)q * 8);
+    float xs0[2], xs1[2];
+#pragma unroll
+    for (int G = 0; G < 2; ++G) {
+      xs0[G] = 2 * c < T ? mx_e8m0(xsc[(size_t)(2 * c) * ng + 2 * q + G]) : 0.f;
+      xs1[G] = 2 * c + 1 < T ? mx_e8m0(xsc[(size_t)(2 * c + 1) * ng + 2 * q + G]) : 0.f;
+    }
+    const uint8_t* xrow = g < T ? xq + (size_t)g * a.inter + 64 * q + 8 * c : nullptr;
+    mx_unit(acc, wv, wsc, xrow, xs0, xs1);
+  }
+  __nv_bfloat16* contrib = reinterpret_cast<__nv_bfloat16*>(a.contrib);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = tile * 16 + g + ((i & 2) ? 8 : 0), t = 2 * c + (i & 1);
+    if (t < T) {
+      const int pick = a.union_pick[u * 32 + t];  // 0: the row did not pick this expert; kk + 1 otherwise
+      if (pick) {
+        const float wgt = pick <= a.topk ? a.topk_w[(size_t)t * a.topk + pick - 1] : 1.0f;
+        contrib[((size_t)(pick - 1) * T + t) * a.hidden + row] = __float2bfloat16_rn(acc[i] * wgt);
+      }
+    }
+  }
+}
+
+cudaError_t launch_mx4_up(const B200Mx4UpArgs& a, cudaStream_t s) {
+  dim3 grid(a.inter / 16, a.union_cap);
+  launch_pdl(mx4_up_kernel, grid, 256, 0, s, a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_mx4_down(const B200Mx4DownArgs& a, cudaStream_t s) {
+  dim3 grid(a.hidden / 16, (a.union_cap + 7) / 8);
+  launch_pdl(mx4_down_kernel, grid, 256, 0, s, a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  return launch_moe_combine(a.contrib, a.residual, a.out, a.rows, a.hidden, a.topk + (a.has_shared ? 1 : 0), s);
+}
+
+}  // namespace b200mono

@@ -368,4 +368,12 @@ cudaError_t launch_moe_down_stream(const B200MoeDownArgs& a, void* contrib, uint
   return cudaGetLastError();
 }
 
+cudaError_t launch_moe_combine(const void* contrib, const void* residual, void* out, int rows, int hidden, int slots,
+                               cudaStream_t s) {
+  const int nvec = rows * (hidden / 8);
+  launch_pdl(moe_combine_kernel, (nvec + 255) / 256, 256, 0, s, (const __nv_bfloat16*)contrib, (const __nv_bfloat16*)residual,
+             (__nv_bfloat16*)out, rows, hidden, slots);
+  return cudaGetLastError();
+}
+
 }  // namespace b200mono

@@ -1,0 +1,120 @@
+"""MXFP4 experts on MXFP8 rows (norm -> router -> row quant -> gate/up + SwiGLU -> row quant -> down + combine) on the
+GPU against the oracle, through the C ABI."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import sgl_amd_mono_b200  # noqa: E402,F401
+from oracle import moe as M  # noqa: E402
+from oracle import quant as Q  # noqa: E402
+from sgl_amd_mono_b200 import cabi, mx4  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def rel(a, b):
+    a, b = a.detach().cpu().double(), b.detach().cpu().double()
+    return ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+
+
+def mx_weights(cfg, seed):
+    g = torch.Generator().manual_seed(seed)
+    H, E, I = cfg["hidden"], cfg["experts"], cfg["inter"]
+    n = E + 1
+    w = dict(norm=(1 + 0.1 * torch.randn(H, generator=g)).bfloat16(), gate_w=(0.02 * torch.randn(E, H, generator=g)).bfloat16(),
+             bias=(0.02 * torch.randn(E, generator=g)).float() if cfg["score_fn"] == 1 else None)
+    w["w13_codes"], w["w13_sc"] = Q.quantize_mxfp4(0.05 * torch.randn(n, 2 * I, H, generator=g))
+    w["w2_codes"], w["w2_sc"] = Q.quantize_mxfp4(0.05 * torch.randn(n, H, I, generator=g))
+    return w
+
+
+# the two MXFP4 configurations' per-rank shapes, scaled down in hidden size and expert count
+CASES = [
+    dict(rows=4, hidden=1024, inter=192, experts=16, topk=4, score_fn=1, has_shared=True, route_scale=2.5, eps=1e-6, swiglu_limit=0.0),
+    dict(rows=8, hidden=2048, inter=512, experts=32, topk=10, score_fn=0, has_shared=True, route_scale=1.0, eps=1e-6, swiglu_limit=7.0),
+    dict(rows=1, hidden=512, inter=64, experts=8, topk=2, score_fn=1, has_shared=True, route_scale=1.0, eps=1e-5, swiglu_limit=0.0),
+]
+
+
+@pytest.mark.parametrize("cfg", CASES, ids=lambda c: f"r{c['rows']}h{c['hidden']}i{c['inter']}e{c['experts']}")
+@pytest.mark.parametrize("rule", ["aiter", "vllm"])
+def test_mx4_block_against_oracle(lib, cfg, rule):
+    rows, H, I, E, K = cfg["rows"], cfg["hidden"], cfg["inter"], cfg["experts"], cfg["topk"]
+    w = mx_weights(cfg, seed=rows)
+    g = torch.Generator().manual_seed(100 + rows)
+    x = torch.randn(rows, H, generator=g).bfloat16()
+    res = torch.randn(rows, H, generator=g).bfloat16()
+    ref = M.moe_ffn_mx4(x, w, cfg, residual=res, add_residual=True, rule=rule)
+    d = lambda t: t.to(DEV)
+    # weights: all experts' rows stacked, packed once
+    w13p, w13s = mx4.pack_mxfp4(w["w13_codes"].reshape(-1, H // 2), w["w13_sc"].reshape(-1, H // 32))
+    w2p, w2s = mx4.pack_mxfp4(w["w2_codes"].reshape(-1, I // 2), w["w2_sc"].reshape(-1, I // 32))
+    w13p, w13s, w2p, w2s = d(w13p), d(w13s), d(w2p), d(w2s)
+    cap = min(rows * K, E) + 1
+    xn = torch.empty(rows, H, dtype=torch.bfloat16, device=DEV)
+    s_out = torch.empty(rows, H, dtype=torch.bfloat16, device=DEV)
+    q8 = torch.empty(rows, H, dtype=torch.uint8, device=DEV)
+    q8s = torch.empty(rows, H // 128, device=DEV)
+    lib.call("norm_quant", cabi.fill("B200NormQuantArgs", x=d(x), residual=d(res), weight=d(w["norm"]), res_out=s_out, y=xn, q=q8,
+                                     q_scale=q8s, rows=rows, hidden=H, eps=cfg["eps"]), stream())
+    logits = torch.empty(rows, E, device=DEV)
+    parts = torch.empty(rows, E, -(-H // 1024), device=DEV)
+    ids = torch.empty(rows, K, dtype=torch.int32, device=DEV)
+    wts = torch.empty(rows, K, device=DEV)
+    ucount = torch.zeros(1, dtype=torch.int32, device=DEV)
+    uids = torch.zeros(E + 1, dtype=torch.int32, device=DEV)
+    pick = torch.zeros(E + 1, 32, dtype=torch.uint8, device=DEV)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    gw, bias = d(w["gate_w"]), None if w["bias"] is None else d(w["bias"])
+    lib.call("router", cabi.fill("B200RouterArgs", x=xn, gate_w=gw, bias=bias, logit_parts=parts, logits=logits, topk_ids=ids,
+                                 topk_w=wts, union_count=ucount, union_ids=uids, union_pick=pick, counter=counter, rows=rows,
+                                 hidden=H, experts=E, topk=K, score_fn=cfg["score_fn"], route_scale=cfg["route_scale"],
+                                 has_shared=1), stream())
+    rl = 0 if rule == "aiter" else 1
+    xq = torch.empty(rows, H, dtype=torch.uint8, device=DEV)
+    xc = torch.empty(rows, H // 32, dtype=torch.uint8, device=DEV)
+    lib.call("quant_mxfp8", cabi.fill("B200QuantMxfp8Args", x=xn, q=xq, q_scale=xc, rows=rows, cols=H, rule=rl), stream())
+    mid = torch.full((cap, rows, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lib.call("mx4_up", cabi.fill("B200Mx4UpArgs", w13=w13p, w13_scale=w13s, xq=xq, x_scale=xc, union_ids=uids, union_count=ucount,
+                                 mid=mid, rows=rows, hidden=H, inter=I, experts=E, union_cap=cap,
+                                 swiglu_limit=cfg["swiglu_limit"]), stream())
+    mq = torch.empty(cap, rows, I, dtype=torch.uint8, device=DEV)
+    mc = torch.empty(cap, rows, I // 32, dtype=torch.uint8, device=DEV)
+    lib.call("quant_mxfp8", cabi.fill("B200QuantMxfp8Args", x=mid, q=mq, q_scale=mc, rows=cap * rows, cols=I, rule=rl), stream())
+    contrib = torch.full((K + 1, rows, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = torch.full((rows, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    lib.call("mx4_down", cabi.fill("B200Mx4DownArgs", w2=w2p, w2_scale=w2s, midq=mq, mid_scale=mc, union_ids=uids,
+                                   union_count=ucount, union_pick=pick, topk_w=wts, contrib=contrib, residual=s_out, out=out,
+                                   rows=rows, hidden=H, inter=I, experts=E, topk=K, has_shared=1, union_cap=cap), stream())
+    torch.cuda.synchronize()
+    # routing and the row quant are bit-exact
+    assert np.array_equal(ids.cpu().numpy(), ref["ids"])
+    assert torch.equal(xq.cpu(), ref["xq"].view(torch.uint8)) and torch.equal(xc.cpu(), ref["xc"])
+    U = int(ucount)
+    assert U == len(ref["union"]) and U <= cap
+    # gate/up + SwiGLU: bf16 values of an FP4 x FP8 product, f32 tensor-core accumulation vs f64
+    for u, e in enumerate(ref["union"].tolist()):
+        assert rel(mid[u], ref["mids"][e]) < 5e-3, (u, e)
+    # the block's output: within the bound stated for FP4/FP8-quantised hidden states
+    assert rel(out, ref["out"]) < 2e-2
+    assert not torch.isnan(contrib).any()
+
+
+def test_mx4_refuses_more_than_eight_rows(lib):
+    z = torch.zeros(64, device=DEV)
+    a = cabi.fill("B200Mx4UpArgs", w13=z, w13_scale=z, xq=z, x_scale=z, union_ids=z, union_count=z, mid=z, rows=9, hidden=512,
+                  inter=64, experts=4, union_cap=5, swiglu_limit=0.0)
+    with pytest.raises(cabi.B200MonoError, match="rows=9"):
+        lib.call("mx4_up", a, stream())

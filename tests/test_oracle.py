@@ -135,3 +135,23 @@ def test_moe_ffn_small_block_properties():
     res = inputs.rows_bf16(3, 256, seed=9)
     rr = M.moe_ffn(x, w, cfg, residual=res, add_residual=True)
     assert torch.equal(rr["s"], (x.float() + res.float()).bfloat16())
+
+
+def test_mxfp4_tile_packing_round_trip_and_positions():
+    import sgl_amd_mono_b200  # noqa: F401
+    from sgl_amd_mono_b200 import mx4
+    g = torch.Generator().manual_seed(0)
+    codes = torch.randint(0, 256, (3, 32, 64), generator=g, dtype=torch.uint8)
+    sc = torch.randint(100, 140, (3, 32, 4), generator=g, dtype=torch.uint8)
+    p, ps = mx4.pack_mxfp4(codes, sc)
+    assert p.shape == (3, 2, 2, 32, 16) and ps.shape == (3, 2, 2, 8, 4)
+    c2, s2 = mx4.unpack_mxfp4(p, ps)
+    assert torch.equal(c2, codes) and torch.equal(s2, sc)
+    # lane (g, c) of tile t, k unit u: group G, row g + 8 * half -> bytes [(2G + half) * 4, +4) = dims 8c .. 8c+7 of the group
+    for t, u, gg, cc, G, half in [(0, 0, 0, 0, 0, 0), (1, 1, 3, 2, 1, 1), (1, 0, 7, 3, 0, 1)]:
+        row, b0 = t * 16 + half * 8 + gg, (64 * u + 32 * G + 8 * cc) // 2
+        assert torch.equal(p[0, t, u, gg * 4 + cc, (2 * G + half) * 4:(2 * G + half) * 4 + 4], codes[0, row, b0:b0 + 4])
+        assert int(ps[0, t, u, gg, 2 * G + half]) == int(sc[0, row, 2 * u + G])
+    import pytest
+    with pytest.raises(ValueError):
+        mx4.pack_mxfp4(codes[:, :24], sc[:, :24])
