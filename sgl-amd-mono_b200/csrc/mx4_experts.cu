@@ -19,28 +19,24 @@ namespace {
 __device__ __forceinline__ uint32_t mx_e2m1x4_to_e4m3x4(uint32_t codes) {
   const uint32_t lut_lo = 0x3c383000u, lut_hi = 0x4c484440u;  // 0, .5, 1, 1.5 | 2, 3, 4, 6 as e4m3
   const uint32_t mag = __byte_perm(lut_lo, lut_hi, codes & 0x7777u);
-  const uint32_t s = codes & 0x8888u;
-  const uint32_t sign = ((s & 0x8u) << 4) | ((s & 0x80u) << 8) | ((s & 0x800u) << 12) | ((s & 0x8000u) << 16);
-  return mag | sign;
+  // sign bits: spread the two code bytes over byte pairs (b0 = b1 = n1n0, b2 = b3 = n3n2); an odd nibble's sign already
+  // sits in bit 7 of its byte, an even nibble's moves there with one shift
+  const uint32_t y = __byte_perm(codes, 0u, 0x1100u);
+  return mag | ((y << 4) & 0x00800080u) | (y & 0x80008000u);
 }
 __device__ __forceinline__ float mx_e8m0(uint32_t code) {
   return code == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(code << 23);
 }
 
 // One k unit (two scale groups) of one 16-row weight tile against 8 activation rows.
-//   wv: the lane's 16 packed bytes; wsc: the tile's scale word of row pair g; xrow: the lane's activation row (g),
-//   already offset to the unit's first dim + 8c (nullptr: row absent); xs0 / xs1: activation scales of columns 2c, 2c+1.
-__device__ __forceinline__ void mx_unit(float (&acc)[4], const uint4 wv, const uint32_t wsc, const uint8_t* xrow,
+//   wv: the lane's 16 packed bytes; wsc: the tile's scale word of row pair g; xb: the lane's activation fragments
+//   (row g, dims 8c..8c+7 of each group; zero for an absent row); xs0 / xs1: activation scales of columns 2c, 2c+1.
+__device__ __forceinline__ void mx_unit(float (&acc)[4], const uint4 wv, const uint32_t wsc, const uint2 (&xb)[2],
                                         const float (&xs0)[2], const float (&xs1)[2]) {
   const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
   for (int G = 0; G < 2; ++G) {
-    uint32_t b0 = 0, b1 = 0;
-    if (xrow) {
-      const uint2 xv = *reinterpret_cast<const uint2*>(xrow + 32 * G);
-      b0 = xv.x;
-      b1 = xv.y;
-    }
+    const uint32_t b0 = xb[G].x, b1 = xb[G].y;
     const uint32_t lo = w[2 * G], hi = w[2 * G + 1];  // row g, row g + 8
     float d[4] = {0.f, 0.f, 0.f, 0.f};
     mma_e4m3_16x8x32(d, mx_e2m1x4_to_e4m3x4(lo & 0xffffu), mx_e2m1x4_to_e4m3x4(hi & 0xffffu), mx_e2m1x4_to_e4m3x4(lo >> 16),
@@ -73,18 +69,45 @@ __global__ __launch_bounds__(256) void mx4_up_kernel(B200Mx4UpArgs a) {
   const uint8_t* xsc = reinterpret_cast<const uint8_t*>(a.x_scale);
   const int ng = a.hidden >> 5;  // scale groups per activation row
   float accg[4] = {0.f, 0.f, 0.f, 0.f}, accu[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int q = warp; q < units; q += 8) {
-    const uint4 vg = ld_stream_u4(wg + (size_t)q * 32), vu = ld_stream_u4(wu + (size_t)q * 32);
-    const uint32_t cg = __ldg(sg + (size_t)q * 8), cu = __ldg(su + (size_t)q * 8);
-    float xs0[2], xs1[2];
+  // four k units per step: their weight lines, scale words and activation scales are all requested before the first MMA
+  constexpr int UN = 4;
+  for (int q0 = warp; q0 < units; q0 += 8 * UN) {
+    uint4 vg[UN], vu[UN];
+    uint32_t cg[UN], cu[UN], x0[UN], x1[UN];
+    uint2 xb[UN][2];
 #pragma unroll
-    for (int G = 0; G < 2; ++G) {
-      xs0[G] = 2 * c < T ? mx_e8m0(xsc[(size_t)(2 * c) * ng + 2 * q + G]) : 0.f;
-      xs1[G] = 2 * c + 1 < T ? mx_e8m0(xsc[(size_t)(2 * c + 1) * ng + 2 * q + G]) : 0.f;
+    for (int n = 0; n < UN; ++n) {
+      const int q = q0 + 8 * n;
+      xb[n][0] = xb[n][1] = make_uint2(0u, 0u);
+      if (q < units) {
+        if (g < T) {
+          const uint8_t* xrow = xq + (size_t)g * a.hidden + 64 * q + 8 * c;
+          xb[n][0] = *reinterpret_cast<const uint2*>(xrow);
+          xb[n][1] = *reinterpret_cast<const uint2*>(xrow + 32);
+        }
+        vg[n] = ld_stream_u4(wg + (size_t)q * 32);
+        vu[n] = ld_stream_u4(wu + (size_t)q * 32);
+        cg[n] = __ldg(sg + (size_t)q * 8);
+        cu[n] = __ldg(su + (size_t)q * 8);
+        // the two groups' scale codes of tokens 2c and 2c + 1: adjacent bytes
+        x0[n] = 2 * c < T ? *reinterpret_cast<const uint16_t*>(xsc + (size_t)(2 * c) * ng + 2 * q) : 0u;
+        x1[n] = 2 * c + 1 < T ? *reinterpret_cast<const uint16_t*>(xsc + (size_t)(2 * c + 1) * ng + 2 * q) : 0u;
+      }
     }
-    const uint8_t* xrow = g < T ? xq + (size_t)g * a.hidden + 64 * q + 8 * c : nullptr;
-    mx_unit(accg, vg, cg, xrow, xs0, xs1);
-    mx_unit(accu, vu, cu, xrow, xs0, xs1);
+#pragma unroll
+    for (int n = 0; n < UN; ++n) {
+      const int q = q0 + 8 * n;
+      if (q < units) {
+        float xs0[2], xs1[2];
+#pragma unroll
+        for (int G = 0; G < 2; ++G) {
+          xs0[G] = 2 * c < T ? mx_e8m0((x0[n] >> (8 * G)) & 0xffu) : 0.f;
+          xs1[G] = 2 * c + 1 < T ? mx_e8m0((x1[n] >> (8 * G)) & 0xffu) : 0.f;
+        }
+        mx_unit(accg, vg[n], cg[n], xb[n], xs0, xs1);
+        mx_unit(accu, vu[n], cu[n], xb[n], xs0, xs1);
+      }
+    }
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -130,17 +153,40 @@ __global__ __launch_bounds__(256) void mx4_down_kernel(B200Mx4DownArgs a) {
   const uint8_t* xq = reinterpret_cast<const uint8_t*>(a.midq) + (size_t)u * T * a.inter;
   const uint8_t* xsc = reinterpret_cast<const uint8_t*>(a.mid_scale) + (size_t)u * T * ng;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int q = 0; q < units; ++q) {
-    const uint4 wv = ld_stream_u4(w2 + (size_t)q * 32);
-    const uint32_t wsc = __ldg(s2 + (size_t)q * 8);
-    float xs0[2], xs1[2];
+  constexpr int UN = 4;
+  for (int q0 = 0; q0 < units; q0 += UN) {
+    uint4 wv[UN];
+    uint32_t wsc[UN], x0[UN], x1[UN];
+    uint2 xb[UN][2];
 #pragma unroll
-    for (int G = 0; G < 2; ++G) {
-      xs0[G] = 2 * c < T ? mx_e8m0(xsc[(size_t)(2 * c) * ng + 2 * q + G]) : 0.f;
-      xs1[G] = 2 * c + 1 < T ? mx_e8m0(xsc[(size_t)(2 * c + 1) * ng + 2 * q + G]) : 0.f;
+    for (int n = 0; n < UN; ++n) {
+      const int q = q0 + n;
+      xb[n][0] = xb[n][1] = make_uint2(0u, 0u);
+      if (q < units) {
+        if (g < T) {
+          const uint8_t* xrow = xq + (size_t)g * a.inter + 64 * q + 8 * c;
+          xb[n][0] = *reinterpret_cast<const uint2*>(xrow);
+          xb[n][1] = *reinterpret_cast<const uint2*>(xrow + 32);
+        }
+        wv[n] = ld_stream_u4(w2 + (size_t)q * 32);
+        wsc[n] = __ldg(s2 + (size_t)q * 8);
+        x0[n] = 2 * c < T ? *reinterpret_cast<const uint16_t*>(xsc + (size_t)(2 * c) * ng + 2 * q) : 0u;
+        x1[n] = 2 * c + 1 < T ? *reinterpret_cast<const uint16_t*>(xsc + (size_t)(2 * c + 1) * ng + 2 * q) : 0u;
+      }
     }
-    const uint8_t* xrow = g < T ? xq + (size_t)g * a.inter + 64 * q + 8 * c : nullptr;
-    mx_unit(acc, wv, wsc, xrow, xs0, xs1);
+#pragma unroll
+    for (int n = 0; n < UN; ++n) {
+      const int q = q0 + n;
+      if (q < units) {
+        float xs0[2], xs1[2];
+#pragma unroll
+        for (int G = 0; G < 2; ++G) {
+          xs0[G] = 2 * c < T ? mx_e8m0((x0[n] >> (8 * G)) & 0xffu) : 0.f;
+          xs1[G] = 2 * c + 1 < T ? mx_e8m0((x1[n] >> (8 * G)) & 0xffu) : 0.f;
+        }
+        mx_unit(acc, wv[n], wsc[n], xb[n], xs0, xs1);
+      }
+    }
   }
   __nv_bfloat16* contrib = reinterpret_cast<__nv_bfloat16*>(a.contrib);
 #pragma unroll

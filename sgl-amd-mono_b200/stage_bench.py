@@ -6,7 +6,8 @@ the launching stream, median of `--reps`.  Prints one JSON line per stage with i
 
 Stages: gqa (dense GQA decode: 8 rows, contexts uniform in [1024, 32768), 8 query heads on 1 KV head, d = 128, and
 16 on 2 with d = 256 at context 8192), gdn (verify chain: 8 requests x 4 tokens, 16 key / 32 value heads; decode:
-8 requests), index (index scores, 8 rows, contexts in [4096, 65536), both kernels), topk (exact top-2048 of them).
+8 requests), index (index scores, 8 rows, contexts in [4096, 65536), both kernels), topk (exact top-2048 of them),
+mx4 (MXFP4 experts on MXFP8 rows: gate/up and down + combine at the two MXFP4 layers' per-rank shapes).
 """
 
 from __future__ import annotations
@@ -139,9 +140,51 @@ def bench_index(lib, reps, flush, with_topk):
         report("exact top-2048", us, int(ctx.sum()) * 4, rows=rows)
 
 
+def bench_mx4(lib, reps, flush):
+    """MXFP4 experts on MXFP8 rows, 8 rows: per-rank shapes of the 160-expert top-8 layer at TP8 (hidden 6144, inter 192)
+    and of the 512-expert top-10 layer at TP1 (hidden 2048, inter 512); random codes, every row picks distinct experts."""
+    from sgl_amd_mono_b200 import mx4
+    g = torch.Generator().manual_seed(9)
+    for name, H, I, E, K in [("mx4 experts h6144 i192 e160 top8", 6144, 192, 160, 8), ("mx4 experts h2048 i512 e512 top10", 2048, 512, 512, 10)]:
+        rows, n = 8, E + 1
+        rnd = lambda *s: torch.randint(0, 256, s, generator=g, dtype=torch.uint8)
+        sc = lambda *s: torch.randint(120, 128, s, generator=g, dtype=torch.uint8)
+        w13p, w13s = mx4.pack_mxfp4(rnd(n * 2 * I, H // 2), sc(n * 2 * I, H // 32))
+        w2p, w2s = mx4.pack_mxfp4(rnd(n * H, I // 2), sc(n * H, I // 32))
+        w13p, w13s, w2p, w2s = w13p.to(DEV), w13s.to(DEV), w2p.to(DEV), w2s.to(DEV)
+        U = min(rows * K, E)
+        ids = torch.randperm(E, generator=g)[:U].sort().values
+        uids = torch.cat([ids, torch.tensor([E])]).to(torch.int32).to(DEV)
+        ucount = torch.tensor([U + 1], dtype=torch.int32, device=DEV)
+        pick = torch.zeros(U + 1, 32, dtype=torch.uint8)
+        for i in range(U):
+            pick[i, i % rows] = i // rows + 1
+        pick[U, :rows] = K + 1
+        pick = pick.to(DEV)
+        cap = U + 1
+        xq = torch.randint(0, 120, (rows, H), generator=g, dtype=torch.uint8).to(DEV)
+        xc = sc(rows, H // 32).to(DEV)
+        mid = torch.empty(cap, rows, I, dtype=torch.bfloat16, device=DEV)
+        mq = torch.randint(0, 120, (cap, rows, I), generator=g, dtype=torch.uint8).to(DEV)
+        mc = sc(cap, rows, I // 32).to(DEV)
+        wts = torch.rand(rows, K, generator=g).to(DEV)
+        contrib = torch.zeros(K + 1, rows, H, dtype=torch.bfloat16, device=DEV)
+        out = torch.empty(rows, H, dtype=torch.bfloat16, device=DEV)
+        up = cabi.fill("B200Mx4UpArgs", w13=w13p, w13_scale=w13s, xq=xq, x_scale=xc, union_ids=uids, union_count=ucount, mid=mid,
+                       rows=rows, hidden=H, inter=I, experts=E, union_cap=cap, swiglu_limit=0.0)
+        dn = cabi.fill("B200Mx4DownArgs", w2=w2p, w2_scale=w2s, midq=mq, mid_scale=mc, union_ids=uids, union_count=ucount,
+                       union_pick=pick, topk_w=wts, contrib=contrib, out=out, rows=rows, hidden=H, inter=I, experts=E, topk=K,
+                       has_shared=1, union_cap=cap)
+        per = H * I // 2 + H * I // 32  # bytes of one [H, I] MXFP4 matrix with scales
+        us = timed(lambda: lib.call("mx4_up", up, stream()), reps, flush)
+        report(name + " gate/up", us, cap * 2 * per, distinct_experts=cap)
+        us = timed(lambda: lib.call("mx4_down", dn, stream()), reps, flush)
+        report(name + " down+combine", us, cap * per, distinct_experts=cap)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--stages", default="gqa,gdn,index,topk")
+    ap.add_argument("--stages", default="gqa,gdn,index,topk,mx4")
     ap.add_argument("--reps", type=int, default=20)
     args = ap.parse_args()
     lib = cabi.lib()
@@ -151,6 +194,8 @@ def main():
         bench_gqa(lib, args.reps, flush)
     if "gdn" in stages:
         bench_gdn(lib, args.reps, flush)
+    if "mx4" in stages:
+        bench_mx4(lib, args.reps, flush)
     if "index" in stages or "topk" in stages:
         bench_index(lib, args.reps, flush, "topk" in stages)
 
