@@ -261,9 +261,9 @@ def run_ours(args):
             with torch.cuda.graph(gr, stream=stream):
                 run_step(layers[li], x_in)
             e2e_graphs.append(gr)
-    # kernels per step: K1 10, K2i 2, K2: attention 2, projections and quants 4, exchanges 2, MoE block 5 (the
+    # kernels per step: K1 9, K2i 2, K2: attention 2, projections and quants 3, exchanges 2, MoE block 5 (the
     # slot-ordered combine runs inside the second exchange)
-    launches_per_step = 6 if args.workload == "ffn" else 25
+    launches_per_step = 6 if args.workload == "ffn" else 23
 
     def barrier():
         if world > 1:

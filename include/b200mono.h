@@ -304,8 +304,8 @@ int b200mono_peer_unmap(void* p);
  * (sgl_amd_mono/deepseek_v41/gfx950/attention/front.py:196-368) and glm53 section 3
  * (sgl_amd_mono/glm53/gfx950/kernel.py:3174-3283). */
 typedef struct {
-  const void* kv_q;          /* e4m3 [rows, 512]: normed latent, per-128 quantised */
-  const float* kv_scale;     /* f32 [rows, 4] */
+  const void* kv_q;          /* e4m3 [rows, 512]: normed latent, per-128 quantised (NULL with kv_norm_w) */
+  const float* kv_scale;     /* f32 [rows, 4] (NULL with kv_norm_w) */
   const void* ya;            /* bf16 [rows, ldya]: output of the fused q_a/kv_a projection */
   const int32_t* positions;  /* int32 [rows] */
   const int32_t* slots;      /* int32 [rows]: cache slot of the row's token (<= 0: pad) */
@@ -315,6 +315,11 @@ typedef struct {
   int32_t rows, ldya;
   int32_t col_rope;          /* first of the 64 key position columns in ya */
   int32_t col_idx;           /* first of the 128 index-key columns in ya */
+  const void* kv_norm_w;     /* optional bf16 [512]: when set, the latent's RMSNorm + per-128 FP8 quant (what
+                              * b200mono_norm_quant gives, bit for bit) runs here on ya[:, col_kv : col_kv + 512]
+                              * and kv_q / kv_scale are not read */
+  int32_t col_kv;
+  float eps;
 } B200KvWriteArgs;
 int b200mono_kv_write(const B200KvWriteArgs* a, void* stream);
 
@@ -394,6 +399,8 @@ typedef struct {
   int32_t rows, k, max_pages, max_chunks; /* max_chunks = ceil(k / 64) */
   float scale;
   int32_t heads;
+  void* o_q;                 /* optional e4m3 [rows, heads, 512]: o_lat quantised per 128 (scale = max(amax, 1e-10) / 448) */
+  float* o_scale;            /* optional f32 [rows, heads * 4], with o_q: what b200mono_quant128 of o_lat would give */
 } B200SparseMlaArgs;
 int b200mono_sparse_mla(const B200SparseMlaArgs* a, void* stream);
 

@@ -188,12 +188,17 @@ int b200mono_moe_down(const B200MoeDownArgs* a, void* stream) {
 }
 
 int b200mono_kv_write(const B200KvWriteArgs* a, void* stream) {
-  REQUIRE(a && a->kv_q && a->kv_scale && a->ya && a->positions && a->slots && a->rope_table && a->kv_cache && a->idx_cache,
-          "kv_write: null pointer");
+  REQUIRE(a && a->ya && a->positions && a->slots && a->rope_table && a->kv_cache && a->idx_cache, "kv_write: null pointer");
+  REQUIRE(a->kv_norm_w || (a->kv_q && a->kv_scale), "kv_write: either kv_norm_w or kv_q + kv_scale");
+  REQUIRE(!a->kv_norm_w || (a->col_kv >= 0 && a->col_kv % 8 == 0 && a->col_kv + 512 <= a->ldya && a->ldya % 8 == 0 &&
+                            aligned(a->ya, 16) && aligned(a->kv_norm_w, 16)),
+          "kv_write: fused norm needs col_kv (%d) and ldya (%d) multiples of 8, ya and kv_norm_w 16-byte aligned", a->col_kv,
+          a->ldya);
   REQUIRE(a->rows >= 1 && a->ldya >= 192 && a->col_rope >= 0 && a->col_rope % 2 == 0 && a->col_rope + 64 <= a->ldya &&
               a->col_idx >= 0 && a->col_idx + 128 <= a->ldya,
           "kv_write: bad column layout (ldya=%d col_rope=%d col_idx=%d)", a->ldya, a->col_rope, a->col_idx);
-  REQUIRE(aligned(a->kv_q, 16) && aligned(a->kv_scale, 16) && aligned(a->kv_cache, 16) && aligned(a->idx_cache, 16),
+  REQUIRE((a->kv_norm_w || (aligned(a->kv_q, 16) && aligned(a->kv_scale, 16))) && aligned(a->kv_cache, 16) &&
+              aligned(a->idx_cache, 16),
           "kv_write: kv_q, kv_scale and the caches must be 16-byte aligned");
   return cuda_status(launch_kv_write(*a, (cudaStream_t)stream), "kv_write");
 }
@@ -239,6 +244,7 @@ int b200mono_sparse_mla(const B200SparseMlaArgs* a, void* stream) {
   REQUIRE(aligned(a->q_lat, 16) && aligned(a->q_rope, 16) && aligned(a->kv_cache, 16) && aligned(a->part_o, 16) &&
               aligned(a->o_lat, 16),
           "sparse_mla: pointers must be 16-byte aligned");
+  REQUIRE((a->o_q == nullptr) == (a->o_scale == nullptr) && (!a->o_q || aligned(a->o_q, 4)), "sparse_mla: o_q and o_scale go together");
   return cuda_status(launch_sparse_mla(*a, (cudaStream_t)stream), "sparse_mla");
 }
 

@@ -46,10 +46,58 @@ __global__ __launch_bounds__(128) void kv_write_kernel(B200KvWriteArgs a) {
   const float* tab = a.rope_table + (size_t)pos * 64;
   const __nv_bfloat16* ya = reinterpret_cast<const __nv_bfloat16*>(a.ya) + (size_t)t * a.ldya;
   uint8_t* rec = reinterpret_cast<uint8_t*>(a.kv_cache) + (size_t)slot * 656;
-  if (warp == 0) {
+  if (a.kv_norm_w) {
+    // RMSNorm + per-128 quant of the 512 latent columns, in the order of norm_quant_kernel: thread v < 64 owns the
+    // 8-column vector v; squares added in column order, lanes in an xor tree, warp sums in warp order
+    __shared__ float warp_part[4];
+    const int tid = threadIdx.x;
+    float sv[8];
+    float ss = 0.f;
+    if (tid < 64) {
+      const uint4 xv = reinterpret_cast<const uint4*>(ya + a.col_kv)[tid];
+      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        sv[2 * j] = bf16_lo(xw[j]);
+        sv[2 * j + 1] = bf16_hi(xw[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(sv[j], sv[j]));
+    }
+    ss = warp_sum_tree(ss);
+    if (lane == 0) warp_part[warp] = ss;
+    __syncthreads();
+    const float tot = __fadd_rn(warp_part[0], warp_part[1]);  // the other warps hold no columns
+    const float rstd = det_rsqrt(__fadd_rn(__fdiv_rn(tot, 512.0f), a.eps));
+    float y[8], amax = 0.f;
+    if (tid < 64) {
+      const uint4 wv = reinterpret_cast<const uint4*>(a.kv_norm_w)[tid];
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float wf = (j & 1) ? bf16_hi(ww[j >> 1]) : bf16_lo(ww[j >> 1]);
+        y[j] = round_bf16(__fmul_rn(__fmul_rn(sv[j], rstd), wf));
+        amax = fmaxf(amax, fabsf(y[j]));
+      }
+    }
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if (tid < 64) {
+      const float scale = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+      float q[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q[j] = fminf(fmaxf(__fdiv_rn(y[j], scale), -448.0f), 448.0f);
+      uint2 packed;
+      packed.x = f32x4_to_e4m3x4(q[0], q[1], q[2], q[3]);
+      packed.y = f32x4_to_e4m3x4(q[4], q[5], q[6], q[7]);
+      reinterpret_cast<uint2*>(rec)[tid] = packed;
+      if ((lane & 15) == 0) reinterpret_cast<float*>(rec + 512)[tid >> 4] = scale;
+    }
+  } else if (warp == 0) {
     reinterpret_cast<uint4*>(rec)[lane] = reinterpret_cast<const uint4*>(a.kv_q)[(size_t)t * 32 + lane];
     if (lane == 0) reinterpret_cast<uint4*>(rec + 512)[0] = reinterpret_cast<const uint4*>(a.kv_scale)[t];
-  } else if (warp == 1) {
+  }
+  if (warp == 1) {
     const float v0 = __bfloat162float(ya[a.col_rope + 2 * lane]), v1 = __bfloat162float(ya[a.col_rope + 2 * lane + 1]);
     float o0, o1;
     rope_pair(v0, v1, tab[lane], tab[32 + lane], o0, o1);

@@ -48,6 +48,11 @@ __device__ __forceinline__ void pdl_enter() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+// The two halves, for a kernel that has work which does not depend on the previous kernel (fetching weights):
+// pdl_trigger() first, the independent work, then pdl_wait() before the first access to anything the previous
+// kernels wrote (or may still read).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---------------------------------------------------------------- e4m3 helpers
 // RNE, saturating to +-448 (never NaN for finite input).

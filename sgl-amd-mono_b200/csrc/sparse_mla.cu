@@ -250,6 +250,17 @@ __global__ __launch_bounds__(128) void sparse_mla_combine_kernel(B200SparseMlaAr
   o.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
   o.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
   reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.o_lat) + ((size_t)t * H + h) * kLat)[threadIdx.x] = o;
+  if (a.o_q) {  // the per-128 FP8 group of the W_UV projection: a warp holds one group (32 threads x 4 values)
+    const float y[4] = {bf16_lo(o.x), bf16_hi(o.x), bf16_lo(o.y), bf16_hi(o.y)};
+    const float amax = warp_max(fmaxf(fmaxf(fabsf(y[0]), fabsf(y[1])), fmaxf(fabsf(y[2]), fabsf(y[3]))));
+    const float sc = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+    float q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = fminf(fmaxf(__fdiv_rn(y[j], sc), -448.0f), 448.0f);
+    reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(a.o_q) + ((size_t)t * H + h) * kLat)[threadIdx.x] =
+        f32x4_to_e4m3x4(q[0], q[1], q[2], q[3]);
+    if ((threadIdx.x & 31) == 0) a.o_scale[((size_t)t * H + h) * 4 + (threadIdx.x >> 5)] = sc;
+  }
 }
 
 cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s) {

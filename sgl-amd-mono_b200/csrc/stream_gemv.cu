@@ -112,7 +112,7 @@ template <int NT, int MODE>
 __global__ __launch_bounds__(kThreads, 1) void stream_kernel(StreamP p, const __grid_constant__ CUtensorMap tm_w,
                                                              const __grid_constant__ CUtensorMap tm_x,
                                                              const __grid_constant__ CUtensorMap tm_xs) {
-  pdl_enter();
+  pdl_trigger();
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int SB = stage_bytes<NT>();
   // layout: [stages x SB][red: 2 buffers][barriers]
@@ -138,18 +138,34 @@ __global__ __launch_bounds__(kThreads, 1) void stream_kernel(StreamP p, const __
   const int KB = p.k >> 7;
   const int nchunks = (p.k + kChunk - 1) / kChunk;
   const int T = p.rows;
-  int total_units;
-  if (MODE == MODE_SWIGLU)
-    total_units = (*p.union_count) * p.tiles;
-  else
-    total_units = p.tiles;
-
   if (warp == kConsumers) {
     // ------------------------------------------------------------ producer (one elected lane issues)
     const uint64_t stream_policy = policy_evict_first();
     const uint64_t keep_policy = policy_evict_last();
-    uint32_t it = 0;
     constexpr uint32_t kTileBytes = 2u * 16u * kChunk + NT * 8u * kChunk + NT * 8u * 32u;
+    // Weights and their scales do not depend on the previous kernel: for plain GEMVs the first ring fill of them is
+    // requested before the dependency wait, so that it overlaps the previous kernel's tail; the activation parts of
+    // those stages follow after the wait (a stage's barrier counts all of its bytes, whoever requests them first).
+    uint32_t pre = 0;
+    if (MODE == MODE_PLAIN && lane == 0) {
+      for (int unit = blockIdx.x; unit < p.tiles && pre < (uint32_t)S; unit += gridDim.x) {
+        const UnitRef u = unit_ref<MODE>(p, unit, KB);
+        for (int c = 0; c < nchunks && pre < (uint32_t)S; ++c, ++pre) {
+          const uint32_t sbytes = (uint32_t)min(8, KB - c * 8) * 4;
+          uint8_t* st = ring + (size_t)pre * SB;
+          mbar_arrive_expect_tx(&full[pre], kTileBytes + 2u * sbytes);
+          const int kcol = c * (kChunk / 4);
+          tma_2d(st, &tm_w, kcol, u.wrow[0], &full[pre], stream_policy);
+          tma_2d(st + 16 * kChunk, &tm_w, kcol, u.wrow[1], &full[pre], stream_policy);
+          bulk_g2s(st + off_wscale<NT>(), u.wsc[0] + c * 8, sbytes, &full[pre], keep_policy);
+          bulk_g2s(st + off_wscale<NT>() + 32, u.wsc[1] + c * 8, sbytes, &full[pre], keep_policy);
+        }
+      }
+    }
+    pre = __shfl_sync(0xffffffffu, pre, 0);
+    pdl_wait();
+    const int total_units = MODE == MODE_SWIGLU ? (*p.union_count) * p.tiles : p.tiles;
+    uint32_t it = 0;
     for (int unit = blockIdx.x; unit < total_units && !abort_flag; unit += gridDim.x) {
       const UnitRef u = unit_ref<MODE>(p, unit, KB);
       for (int c = 0; c < nchunks; ++c, ++it) {
@@ -161,19 +177,26 @@ __global__ __launch_bounds__(kThreads, 1) void stream_kernel(StreamP p, const __
           const uint32_t nkb = (uint32_t)min(8, KB - c * 8);
           const uint32_t sbytes = nkb * 4;  // one f32 scale per k block
           uint8_t* st = ring + (size_t)s * SB;
-          mbar_arrive_expect_tx(&full[s], kTileBytes + 2u * sbytes);
           const int kcol = c * (kChunk / 4);  // u32 column
-          tma_2d(st, &tm_w, kcol, u.wrow[0], &full[s], stream_policy);
-          tma_2d(st + 16 * kChunk, &tm_w, kcol, u.wrow[1], &full[s], stream_policy);
+          if (it >= pre) {
+            mbar_arrive_expect_tx(&full[s], kTileBytes + 2u * sbytes);
+            tma_2d(st, &tm_w, kcol, u.wrow[0], &full[s], stream_policy);
+            tma_2d(st + 16 * kChunk, &tm_w, kcol, u.wrow[1], &full[s], stream_policy);
+            bulk_g2s(st + off_wscale<NT>(), u.wsc[0] + c * 8, sbytes, &full[s], keep_policy);
+            bulk_g2s(st + off_wscale<NT>() + 32, u.wsc[1] + c * 8, sbytes, &full[s], keep_policy);
+          }
           tma_2d(st + 32 * kChunk, &tm_x, u.group * (p.k / 4) + kcol, 0, &full[s], keep_policy);
           tma_2d(st + off_xscale<NT>(), &tm_xs, u.group * KB + c * 8, 0, &full[s], keep_policy);
-          bulk_g2s(st + off_wscale<NT>(), u.wsc[0] + c * 8, sbytes, &full[s], keep_policy);
-          bulk_g2s(st + off_wscale<NT>() + 32, u.wsc[1] + c * 8, sbytes, &full[s], keep_policy);
         }
         __syncwarp();
       }
     }
     // drain: every stage armed but not yet consumed still has copies in flight towards this CTA
+    if (abort_flag && it < pre) {  // early weight requests whose activation part was never issued: let them land
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 50000ull) {
+      }
+    }
     if (abort_flag) {
       const uint32_t first = it > (uint32_t)S ? it - S : 0;
       for (uint32_t i = first; i < it; ++i) {
@@ -186,6 +209,8 @@ __global__ __launch_bounds__(kThreads, 1) void stream_kernel(StreamP p, const __
   }
 
   // -------------------------------------------------------------- consumers
+  pdl_wait();
+  const int total_units = MODE == MODE_SWIGLU ? (*p.union_count) * p.tiles : p.tiles;
   const int g = lane >> 2, c4 = lane & 3;
   uint32_t it = 0;
   int buf = 0;

@@ -161,11 +161,11 @@ class LayerRunner:
     def _k1_index(self, rows: int, step: Step):
         """The branch the indexer waits for: KV record and index key of the new tokens, index query records."""
         w, c = self.w, self.c
-        self._norm_quant(self.ya[:, COL_KV:], w.kv_norm, self.kv_q, self.kv_s, rows, KV_LORA, x_stride=YA_COLS)
-        self.lib.call("kv_write", cabi.fill("B200KvWriteArgs", kv_q=self.kv_q, kv_scale=self.kv_s, ya=self.ya,
-                                            positions=step.positions, slots=step.slots, rope_table=c.rope_table,
-                                            kv_cache=c.kv, idx_cache=c.idx, rows=rows, ldya=YA_COLS, col_rope=COL_ROPE,
-                                            col_idx=COL_IDX), self._s)
+        # the latent's RMSNorm + FP8 quant runs inside the record write
+        self.lib.call("kv_write", cabi.fill("B200KvWriteArgs", ya=self.ya, positions=step.positions, slots=step.slots,
+                                            rope_table=c.rope_table, kv_cache=c.kv, idx_cache=c.idx, rows=rows, ldya=YA_COLS,
+                                            col_rope=COL_ROPE, col_idx=COL_IDX, kv_norm_w=w.kv_norm, col_kv=COL_KV,
+                                            eps=self.b.eps), self._s)
         self._gemv(w.wiq_b, w.wiq_b_s, self.qa_q, self.qa_s, self.qi, rows, IDX_HEADS * IDX_DIM, Q_LORA)
         self.lib.call("idx_q_post", cabi.fill("B200IdxQPostArgs", qi=self.qi, ya=self.ya, positions=step.positions,
                                               rope_table=c.rope_table, q_rec=self.q_rec, w=self.iw, rows=rows, heads=IDX_HEADS,
@@ -205,8 +205,8 @@ class LayerRunner:
                                               page_table=step.page_table, req_of_row=step.req_of_row, topk_idx=self.topk_idx,
                                               topk_count=self.topk_count, part_o=self.part_o, part_ml=self.part_ml,
                                               o_lat=self.o_lat, rows=rows, k=TOPK_KEYS, max_pages=step.page_table.shape[1],
-                                              max_chunks=self.chunks, scale=192 ** -0.5, heads=hl), self._s)
-        self._quant(self.o_lat, self.ol_q, self.ol_s, rows, hl * KV_LORA)
+                                              max_chunks=self.chunks, scale=192 ** -0.5, heads=hl, o_q=self.ol_q,
+                                              o_scale=self.ol_s), self._s)  # the merge also writes W_UV's FP8 groups
         self._gemv(w.w_uv, w.w_uv_s, self.ol_q, self.ol_s, self.o_h, rows, hl * V_HEAD, KV_LORA, groups=hl)
         self._quant(self.o_h, self.oh_q, self.oh_s, rows, hl * V_HEAD)
         self._gemv(w.w_o, w.w_o_s, self.oh_q, self.oh_s, self.attn_part, rows, b.hidden, hl * V_HEAD)

@@ -28,7 +28,8 @@ def i32(x):
     return torch.tensor(x, dtype=torch.int32, device=DEV)
 
 
-def test_kv_and_index_records_bit_exact(lib):
+@pytest.mark.parametrize("fused", [False, True])  # latent norm + quant as its own launch, or inside the record write
+def test_kv_and_index_records_bit_exact(lib, fused):
     rows, ldya, eps = 6, 2304, 1e-6
     g = torch.Generator().manual_seed(1)
     ya = (torch.randn(rows, ldya, generator=g) * 2).bfloat16()
@@ -43,14 +44,20 @@ def test_kv_and_index_records_bit_exact(lib):
     yad, wd = ya.to(DEV), wkv.to(DEV)
     kv_q = torch.zeros(rows, 512, dtype=torch.uint8, device=DEV)
     kv_s = torch.zeros(rows, 4, device=DEV)
-    lib.call("norm_quant", cabi.fill("B200NormQuantArgs", x=yad[:, 1536:], weight=wd, q=kv_q, q_scale=kv_s, rows=rows,
-                                     hidden=512, eps=eps, x_stride=ldya), stream())
-    lib.call("kv_write", cabi.fill("B200KvWriteArgs", kv_q=kv_q, kv_scale=kv_s, ya=yad, positions=pos.to(DEV),
-                                   slots=slots.to(DEV), rope_table=table.to(DEV), kv_cache=kv_cache, idx_cache=idx_cache,
-                                   rows=rows, ldya=ldya, col_rope=2048, col_idx=2112), stream())
+    if fused:
+        lib.call("kv_write", cabi.fill("B200KvWriteArgs", ya=yad, positions=pos.to(DEV), slots=slots.to(DEV),
+                                       rope_table=table.to(DEV), kv_cache=kv_cache, idx_cache=idx_cache, rows=rows, ldya=ldya,
+                                       col_rope=2048, col_idx=2112, kv_norm_w=wd, col_kv=1536, eps=eps), stream())
+    else:
+        lib.call("norm_quant", cabi.fill("B200NormQuantArgs", x=yad[:, 1536:], weight=wd, q=kv_q, q_scale=kv_s, rows=rows,
+                                         hidden=512, eps=eps, x_stride=ldya), stream())
+        lib.call("kv_write", cabi.fill("B200KvWriteArgs", kv_q=kv_q, kv_scale=kv_s, ya=yad, positions=pos.to(DEV),
+                                       slots=slots.to(DEV), rope_table=table.to(DEV), kv_cache=kv_cache, idx_cache=idx_cache,
+                                       rows=rows, ldya=ldya, col_rope=2048, col_idx=2112), stream())
     torch.cuda.synchronize()
     _, _, q_ref, s_ref = M.rmsnorm_quant(ya[:, 1536:2048].contiguous(), wkv, eps)
-    assert torch.equal(kv_q.cpu(), q_ref.view(torch.uint8)) and torch.equal(kv_s.cpu(), s_ref)
+    if not fused:
+        assert torch.equal(kv_q.cpu(), q_ref.view(torch.uint8)) and torch.equal(kv_s.cpu(), s_ref)
     rec_ref = A.kv_record(q_ref, s_ref, A.rope_gptj(ya[:, 2048:2112].contiguous(), pos, table))
     k = ya[:, 2112:2240].clone()
     k[:, 64:] = A.rope_gptj(k[:, 64:].contiguous(), pos, table)
@@ -209,11 +216,17 @@ def test_sparse_mla_against_oracle(lib, n_sel):
     part_o = torch.full((rows, chunks, 16, 512), float("nan"), dtype=torch.bfloat16, device=DEV)
     part_ml = torch.full((rows, chunks, 16, 2), float("nan"), device=DEV)
     o = torch.full((rows, 16, 512), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o_q = torch.zeros(rows, 16, 512, dtype=torch.uint8, device=DEV)
+    o_s = torch.full((rows, 64), float("nan"), device=DEV)
     lib.call("sparse_mla", cabi.fill("B200SparseMlaArgs", q_lat=q_lat.to(DEV), q_rope=q_rope.to(DEV), kv_cache=cache.to(DEV),
                                      page_table=table.to(DEV), req_of_row=i32(list(range(rows))), topk_idx=sel.to(DEV),
                                      topk_count=i32(n_sel), part_o=part_o, part_ml=part_ml, o_lat=o, rows=rows, k=k,
-                                     max_pages=max_pages, max_chunks=chunks, scale=scale, heads=16), stream())
+                                     max_pages=max_pages, max_chunks=chunks, scale=scale, heads=16, o_q=o_q, o_scale=o_s),
+             stream())
     torch.cuda.synchronize()
+    # the fused FP8 groups are exactly the per-128 quant of the launch's own bf16 output
+    rq, rs = Q.quant128(o.cpu().view(rows, 16 * 512))
+    assert torch.equal(o_q.cpu().view(rows, -1), rq.view(torch.uint8)) and torch.equal(o_s.cpu(), rs)
     for t in range(rows):
         pos = sel[t, : n_sel[t]].long()
         slots = table[t, pos // 64].long() * 64 + pos % 64
