@@ -329,14 +329,14 @@ __global__ __cluster_dims__(kTopkCluster, 1, 1) __launch_bounds__(1024) void top
     key[j] = i < n ? radix_key(__ldcg(sc + i)) : 0u;
   }
   unsigned prefix = 0, need = (unsigned)a.k;
+  if (tid < 512) (&hist[0][0])[tid] = 0;
+  __syncthreads();
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
     const unsigned mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
-    // local histogram of this pass, straight into the buffer the peers will read: lanes with the same digit
-    // elect one to add their count (scores cluster in a few digits), warps without a candidate skip the match
+    // local histogram of this pass, straight into the buffer the peers will read (zeroed two passes ago): lanes with
+    // the same digit elect one to add their count (scores cluster in a few digits), warps without a candidate skip
     unsigned int* hl = hist[pass & 1];
-    if (tid < 256) hl[tid] = 0;
-    __syncthreads();
 #pragma unroll
     for (int j = 0; j < kTopkPer; ++j) {
       const int i = base + j * 1024 + tid;
@@ -356,9 +356,13 @@ __global__ __cluster_dims__(kTopkCluster, 1, 1) __launch_bounds__(1024) void top
       unsigned c = 0;
       for (uint32_t r = 0; r < kTopkCluster; ++r) c += dsmem_ld_u32(&hl[tid], r);
       ghist[tid] = c;
+    } else if (tid < 512) {
+      // the other buffer was read by the peers during the previous pass, which every CTA has left: clear it for the next
+      hist[(pass & 1) ^ 1][tid - 256] = 0;
     }
     __syncthreads();
-    __shared__ unsigned int s_found[2];
+    __shared__ unsigned int s_found_buf[2][2];
+    unsigned int* s_found = s_found_buf[pass & 1];
     if (warp == 0) {
       unsigned run = 0;
       int found = -1;
@@ -385,9 +389,8 @@ __global__ __cluster_dims__(kTopkCluster, 1, 1) __launch_bounds__(1024) void top
       }
     }
     __syncthreads();
-    prefix |= s_found[0] << shift;
+    prefix |= s_found[0] << shift;  // this pass's slot is written again two passes (four barriers) later
     need = s_found[1];
-    __syncthreads();
   }
   const unsigned thr = prefix, need_eq = need;
   // per (chunk, warp) counts of this CTA's keys above / equal to the threshold
