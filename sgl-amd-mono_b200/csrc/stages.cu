@@ -46,8 +46,29 @@ __global__ __launch_bounds__(256) void norm_quant_kernel(B200NormQuantArgs a) {
     }
   };
 
+  // the thread's first kKeep vectors stay in registers between the two passes (hidden <= 8192: all of them), and the
+  // norm weights are requested before the reduction so that their latency hides behind it
+  constexpr int kKeep = 4;
+  float keep[kKeep][8];
+  uint4 wkeep[kKeep];
   float ss = 0.f;
-  for (int v = tid; v < nvec; v += 256) {
+#pragma unroll
+  for (int k = 0; k < kKeep; ++k) {
+    const int v = tid + 256 * k;
+    if (v < nvec) {
+      load_s(v, keep[k]);
+      wkeep[k] = w[v];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kKeep; ++k) {
+    const int v = tid + 256 * k;
+    if (v < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = __fadd_rn(ss, __fmul_rn(keep[k][j], keep[k][j]));
+    }
+  }
+  for (int v = tid + 256 * kKeep; v < nvec; v += 256) {
     float s[8];
     load_s(v, s);
 #pragma unroll
@@ -62,15 +83,27 @@ __global__ __launch_bounds__(256) void norm_quant_kernel(B200NormQuantArgs a) {
   const float var = __fdiv_rn(tot, (float)a.hidden);
   const float rstd = det_rsqrt(__fadd_rn(var, a.eps));
 
-  for (int v0 = warp * 32; v0 < nvec; v0 += 256) {
-    const int v = v0 + lane;
+  int kidx = 0;
+  for (int v0 = warp * 32; v0 < nvec; v0 += 256, ++kidx) {
+    const int v = v0 + lane;  // = tid + 256 * kidx: the vector this thread summed in the first pass
     const bool ok = v < nvec;
     float y[8];
     float amax = 0.f;
     if (ok) {
       float s[8];
-      load_s(v, s);
-      uint4 wv = w[v];
+      uint4 wv;
+      if (kidx < kKeep) {
+#pragma unroll
+        for (int k = 0; k < kKeep; ++k)
+          if (k == kidx) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j] = keep[k][j];
+            wv = wkeep[k];
+          }
+      } else {
+        load_s(v, s);
+        wv = w[v];
+      }
       const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
       uint32_t res_bits[4], y_bits[4];
 #pragma unroll
