@@ -42,6 +42,66 @@ def peaks():
         return 6650.0, "fallback"
 
 
+class NvmlSampler:
+    """SM clock and throttle reasons read through NVML every 10 ms by a thread while the timed region runs (read-only
+    queries).  The timed region of a short run lasts tens of milliseconds: too short for an nvidia-smi process to
+    start and report, which is what ClockSampler below does when NVML's Python binding is missing."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
+
+    def __init__(self, index: int):
+        import threading
+
+        import pynvml
+        self.nv = pynvml
+        pynvml.nvmlInit()
+        # torch's device index counts visible devices; NVML wants the physical one
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        phys = index
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if index < len(ids) and ids[index].isdigit():
+                phys = int(ids[index])
+        self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+        self.sm, self.mask, self.stop = [], 0, threading.Event()
+        self.thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        nv = self.nv
+        while not self.stop.is_set():
+            try:
+                self.sm.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+            except Exception:
+                pass
+            self.stop.wait(0.01)
+
+    def __enter__(self):
+        self.thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self.stop.set()
+        self.thread.join(timeout=2)
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": len(self.sm), "source": "nvml, 10 ms"}
+        try:
+            out["sm_mhz"] = float(statistics.median(self.sm)) if self.sm else None
+            out["sm_max_mhz"] = float(self.nv.nvmlDeviceGetMaxClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            out["reasons"] = sorted(nm for bit, nm in self.REASONS.items() if self.mask & bit)
+        except Exception:
+            pass
+        return out
+
+
+def clock_sampler(index: int):
+    try:
+        return NvmlSampler(index)
+    except Exception:
+        return ClockSampler(index)
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons while the timed region runs."""
 
@@ -293,7 +353,7 @@ def run_ours(args):
 
     step_fn = lambda i: graphs[i % len(graphs)].replay()  # noqa: E731
     timed(step_fn, args.warmup)
-    with ClockSampler(local) as cs:
+    with clock_sampler(local) as cs:
         ms = timed(step_fn, args.steps)
     clocks = cs.summary()
     us_per_step = ms * 1000.0 / args.steps
