@@ -53,18 +53,19 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
   const int* sel = a.topk_idx + (size_t)t * a.k + e0;
 
   // ---- gather + dequantise: warp w takes keys 16w .. 16w+15.  Lane j < 16 resolves key j's cache slot (selection
-  // -> page table), then the records are fetched four keys at a time so that their loads overlap.
+  // -> page table), then the records are fetched eight keys at a time so that their loads overlap.
   size_t my_slot = 0;
   if (lane < 16 && warp * 16 + lane < n_here) {
     const int pos = sel[warp * 16 + lane];
     my_slot = (size_t)pages[pos >> 6] * 64 + (pos & 63);
   }
+  constexpr int GB = 8;  // keys per batch
 #pragma unroll 1
-  for (int j0 = 0; j0 < 16; j0 += 4) {
-    uint4 lat16[4], rope16[4];
-    float scale[4];
+  for (int j0 = 0; j0 < 16; j0 += GB) {
+    uint4 lat16[GB], rope16[GB];
+    float scale[GB];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < GB; ++u) {
       const int key = warp * 16 + j0 + u;
       const size_t slot = __shfl_sync(0xffffffffu, my_slot, j0 + u);
       lat16[u] = make_uint4(0, 0, 0, 0);
@@ -78,7 +79,7 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < GB; ++u) {
       const int key = warp * 16 + j0 + u;
       const uint32_t w4[4] = {lat16[u].x, lat16[u].y, lat16[u].z, lat16[u].w};
       uint32_t o[8];

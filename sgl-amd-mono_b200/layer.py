@@ -126,6 +126,7 @@ class LayerRunner:
         self.oh_q, self.oh_s = buf((W, hl * V_HEAD), u8), buf((W, hl), f32)
         self.attn_part = buf((W, b.hidden), bf)
         self.a = buf((W, b.hidden), bf)       # residual stream after attention
+        self.ffn_part = buf((W, b.hidden), bf)  # this rank's MoE partial rows (steps wider than 8 rows)
         self.status = buf((4,), i32)
         self.overlap = True
         self.side = torch.cuda.Stream(dev)
@@ -212,19 +213,28 @@ class LayerRunner:
         self._gemv(w.w_o, w.w_o_s, self.oh_q, self.oh_s, self.attn_part, rows, b.hidden, hl * V_HEAD)
         a = self.a[:rows]
         self.reducer.run(self.attn_part[:rows], x, a, stream=st)
-        # MoE block on the reduced stream; its slot-ordered combine is fused into the second all-reduce
-        calls = self.ffn.stage_calls(a, out, None, False)
-        for name, args in calls[:-1]:
-            self.lib.call(name, args, self._s)
-        name, dn = calls[-1]
-        dn.variant = 2
-        dn.skip_combine = 1  # the all-reduce sums the slots
-        self.lib.call(name, dn, self._s)
-        L = self.ffn.step_layout
-        slots = b.topk + 1
-        contrib = self.ffn.scratch[L.contrib: L.contrib + slots * rows * b.hidden * 2].view(torch.bfloat16).view(
-            slots, rows, b.hidden)
-        self.reducer.run(contrib, a, out, slots=slots, stream=st)
+        inter_local = b.inter // b.tp
+        if rows <= 8 and inter_local % 256 == 0 and inter_local <= 2048:
+            # MoE block on the reduced stream; its slot-ordered combine is fused into the second all-reduce
+            calls = self.ffn.stage_calls(a, out, None, False)
+            for name, args in calls[:-1]:
+                self.lib.call(name, args, self._s)
+            name, dn = calls[-1]
+            dn.variant = 2
+            dn.skip_combine = 1  # the all-reduce sums the slots
+            self.lib.call(name, dn, self._s)
+            L = self.ffn.step_layout
+            slots = b.topk + 1
+            contrib = self.ffn.scratch[L.contrib: L.contrib + slots * rows * b.hidden * 2].view(torch.bfloat16).view(
+                slots, rows, b.hidden)
+            self.reducer.run(contrib, a, out, slots=slots, stream=st)
+        else:
+            # more than 8 rows (or an expert slice the persistent down projection does not take): the block combines its
+            # own slots into this rank's partial rows, which the second all-reduce then sums with the residual
+            part = self.ffn_part[:rows]
+            for name, args in self.ffn.stage_calls(a, part, None, False):
+                self.lib.call(name, args, self._s)
+            self.reducer.run(part, a, out, stream=st)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: Step, stream=None):
         """K1, K2i, K2.  With `overlap` (default) the indexer branch (KV / index records, index queries, scores, top-k)

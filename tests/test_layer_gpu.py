@@ -35,7 +35,8 @@ def build_runner(cfg, w, caches, width):
     return LayerRunner(b, lw, Caches(kv=caches["kv"], idx=caches["idx"], rope_table=caches["rope_table"]), device=DEV, world=1)
 
 
-@pytest.mark.parametrize("rows,tokens_per_request,ctx", [(4, 1, (4096, 9000)), (8, 4, (2040, 2060)), (3, 1, (1, 300))])
+@pytest.mark.parametrize("rows,tokens_per_request,ctx", [(4, 1, (4096, 9000)), (8, 4, (2040, 2060)), (3, 1, (1, 300)),
+                                                        (32, 4, (2500, 6000))])  # the last: a 32-row verify step
 def test_layer_shard_against_oracle(lib, rows, tokens_per_request, ctx):
     # rank 0's shard of the TP8 layer (16 heads, expert slices of 256) run alone
     cfg = L.layer_cfg(tp=8, experts=64, max_ctx=16384)
@@ -85,9 +86,15 @@ def test_layer_shard_against_oracle(lib, rows, tokens_per_request, ctx):
     assert rel(out, C.allreduce([ffn_ref["out"]], r.a[:rows])) < 2e-2
 
     # ---- end to end from the same inputs
+    # (the stage checks above consume the launch's own intermediates; here the oracle also makes its own selections,
+    # and a key near the top-2048 threshold may fall on the other side for a row, which moves that row's attention
+    # output: the typical row is held to the 2e-2 bound, the whole step to the reference's own layer bound of 5e-2,
+    # sgl_amd_mono/deepseek_v4/spec.py:146-153)
     ref = L.forward(x, [w], cpu_caches0, cs, cfg)
+    per_row = sorted(rel(out[t], ref["out"][t]) for t in range(rows))
+    assert per_row[rows // 2] < 2e-2, per_row
     e = rel(out, ref["out"])
-    assert e < 2e-2, e
+    assert e < (2e-2 if rows <= 8 else 5e-2), e
     # rows are independent of each other: a verify row sees its earlier siblings through the cache only
     assert not torch.isnan(out.float()).any()
 
@@ -105,3 +112,55 @@ def test_layer_two_ranks_over_cuda_ipc():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "layer ok" in r.stdout
+
+
+def test_three_layer_stack_in_one_graph(lib):
+    """Layers with their own weights and caches, one shared exchange buffer, chained inside one CUDA graph: the replay is
+    bitwise the eager chain (exchange epochs and arrival counters live on the device and carry over from layer to layer
+    and from replay to replay), and the chain follows the oracle's."""
+    rows, n_layers = 4, 3
+    cfg = L.layer_cfg(tp=8, experts=32, max_ctx=8192)
+    caches0, step = L.make_step(cfg, rows, 2000, 4000, seed=11, tokens_per_request=1, device=DEV)
+    cs = {k: v.cpu() for k, v in step.items()}
+    ws = [L.make_weights(cfg, rank=0, seed=20 + i, device=DEV) for i in range(n_layers)]
+    layer_caches = [{k: v.clone() for k, v in caches0.items()} for _ in range(n_layers)]
+    runners = []
+    for i in range(n_layers):
+        r = build_runner(cfg, ws[i], layer_caches[i], rows)
+        if runners:  # one exchange buffer for the stack
+            r.reducer = runners[0].reducer
+        runners.append(r)
+    st = Step(**step)
+    x0 = torch.randn(rows, cfg["hidden"], generator=torch.Generator().manual_seed(3)).bfloat16().to(DEV)
+    bufs = [torch.empty_like(x0) for _ in range(n_layers)]
+
+    def chain():
+        x = x0
+        for r, o in zip(runners, bufs):
+            r.forward(x, o, st)
+            x = o
+
+    chain()
+    torch.cuda.synchronize()
+    eager = bufs[-1].clone()
+    s = torch.cuda.Stream(DEV)
+    with torch.cuda.stream(s):
+        chain()
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            chain()
+        for _ in range(3):
+            bufs[-1].fill_(float("nan"))
+            g.replay()
+            s.synchronize()
+            assert torch.equal(bufs[-1], eager), "replay differs from the eager chain"
+    for r in runners:
+        assert r.reducer.status() == 0 and r.ffn.status() == 0 and int(r.status[0].item()) == 0
+    # every layer against the oracle's layer run from that layer's own input (the chain's hidden states are not
+    # contractive with random weights, so errors are not compared across layers)
+    x = x0.cpu()
+    for i in range(n_layers):
+        ref = L.forward(x, [ws[i]], {k: v.cpu().clone() for k, v in caches0.items()}, cs, cfg)
+        assert rel(bufs[i], ref["out"]) < 2e-2, i
+        x = bufs[i].cpu()
