@@ -1,7 +1,7 @@
 // Sparse MLA decode over the selected FP8 latent entries (flash decoding, split + combine).
 //
-// Split: task = (row, chunk of 64 selected entries); the local heads are taken 16 at a time (one MMA M
-//   tile) over the same gathered entries.
+// Split: task = (row, chunk of 64 selected entries, up to four head slices); 8 warps; the slice's heads are taken
+//   16 at a time (one MMA M tile) over the same gathered entries.
 //   gather the 64 paged records, dequantise e4m3 * scale -> bf16 into shared memory,
 //   S = Q K^T on bf16 tensor cores (k = 512 latent + 64 position dims), split-local softmax
 //   (own max m, sum l of the unrounded probabilities), P rounded to bf16, O = P V with V = the
@@ -37,7 +37,7 @@ struct MlaSmem {
   float s[kMlaHeads][kChunkKeys];
 };
 
-__global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs a) {
+__global__ __launch_bounds__(256) void sparse_mla_split_kernel(B200SparseMlaArgs a) {
   pdl_enter();
   extern __shared__ __align__(16) uint8_t raw[];
   MlaSmem& sm = *reinterpret_cast<MlaSmem*>(raw);
@@ -52,21 +52,21 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
   const int* pages = a.page_table + (size_t)req * a.max_pages;
   const int* sel = a.topk_idx + (size_t)t * a.k + e0;
 
-  // ---- gather + dequantise: warp w takes keys 16w .. 16w+15.  Lane j < 16 resolves key j's cache slot (selection
-  // -> page table), then the records are fetched eight keys at a time so that their loads overlap.
+  // ---- gather + dequantise: warp w (of 8) takes keys 8w .. 8w+7.  Lane j < 8 resolves key j's cache slot (selection
+  // -> page table), then the eight records are fetched together so that their loads overlap.
   size_t my_slot = 0;
-  if (lane < 16 && warp * 16 + lane < n_here) {
-    const int pos = sel[warp * 16 + lane];
+  if (lane < 8 && warp * 8 + lane < n_here) {
+    const int pos = sel[warp * 8 + lane];
     my_slot = (size_t)pages[pos >> 6] * 64 + (pos & 63);
   }
-  constexpr int GB = 8;  // keys per batch
-#pragma unroll 1
-  for (int j0 = 0; j0 < 16; j0 += GB) {
+  constexpr int GB = 8;  // keys per warp
+  {
+    const int j0 = 0;
     uint4 lat16[GB], rope16[GB];
     float scale[GB];
 #pragma unroll
     for (int u = 0; u < GB; ++u) {
-      const int key = warp * 16 + j0 + u;
+      const int key = warp * GB + j0 + u;
       const size_t slot = __shfl_sync(0xffffffffu, my_slot, j0 + u);
       lat16[u] = make_uint4(0, 0, 0, 0);
       rope16[u] = make_uint4(0, 0, 0, 0);
@@ -80,7 +80,7 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
     }
 #pragma unroll
     for (int u = 0; u < GB; ++u) {
-      const int key = warp * 16 + j0 + u;
+      const int key = warp * GB + j0 + u;
       const uint32_t w4[4] = {lat16[u].x, lat16[u].y, lat16[u].z, lat16[u].w};
       uint32_t o[8];
 #pragma unroll
@@ -95,60 +95,54 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
       if (lane < 8) *reinterpret_cast<uint4*>(&sm.rope[key][lane * 8]) = rope16[u];
     }
   }
-  // the gathered entries serve every group of 16 heads in turn (hg)
-  for (int hg = 0; hg < H / kMlaHeads; ++hg) {
+  // the gathered entries serve every group of 16 heads this CTA takes (hg = blockIdx.z, + gridDim.z, ...)
+  for (int hg = blockIdx.z; hg < H / kMlaHeads; hg += gridDim.z) {
   // ---- queries: [16][512 latent | 64 position] bf16
   {
     const uint4* ql = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_lat) + ((size_t)t * H + hg * kMlaHeads) * kLat);
-    for (int i = threadIdx.x; i < kMlaHeads * kLat / 8; i += 128) {
+    for (int i = threadIdx.x; i < kMlaHeads * kLat / 8; i += 256) {
       const int h = i / (kLat / 8), v = i % (kLat / 8);
       *reinterpret_cast<uint4*>(&sm.q[h][v * 8]) = ql[i];
     }
     const uint4* qr = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_rope) + ((size_t)t * H + hg * kMlaHeads) * kRope);
-    for (int i = threadIdx.x; i < kMlaHeads * kRope / 8; i += 128) {
+    for (int i = threadIdx.x; i < kMlaHeads * kRope / 8; i += 256) {
       const int h = i / (kRope / 8), v = i % (kRope / 8);
       *reinterpret_cast<uint4*>(&sm.q[h][kLat + v * 8]) = qr[i];
     }
   }
   __syncthreads();
 
-  // ---- S = Q K^T: warp w owns key tiles 2w, 2w+1 (8 keys each)
+  // ---- S = Q K^T: warp w owns key tile w (8 keys)
   {
-    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-    const int n0 = warp * 16;
+    float s0[4] = {0.f, 0.f, 0.f, 0.f};
+    const int n0 = warp * 8;
 #pragma unroll 4
     for (int k0 = 0; k0 < kLat + kRope; k0 += 16) {
       const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sm.q[g][k0 + 2 * c]);
       const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sm.q[g + 8][k0 + 2 * c]);
       const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sm.q[g][k0 + 2 * c + 8]);
       const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sm.q[g + 8][k0 + 2 * c + 8]);
-      uint32_t b0, b1, b2, b3;
+      uint32_t b0, b1;
       if (k0 < kLat) {
         b0 = *reinterpret_cast<const uint32_t*>(&sm.lat[n0 + g][k0 + 2 * c]);
         b1 = *reinterpret_cast<const uint32_t*>(&sm.lat[n0 + g][k0 + 2 * c + 8]);
-        b2 = *reinterpret_cast<const uint32_t*>(&sm.lat[n0 + 8 + g][k0 + 2 * c]);
-        b3 = *reinterpret_cast<const uint32_t*>(&sm.lat[n0 + 8 + g][k0 + 2 * c + 8]);
       } else {
         const int kr = k0 - kLat;
         b0 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + g][kr + 2 * c]);
         b1 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + g][kr + 2 * c + 8]);
-        b2 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + 8 + g][kr + 2 * c]);
-        b3 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + 8 + g][kr + 2 * c + 8]);
       }
       mma_bf16_16x8x16(s0, a0, a1, a2, a3, b0, b1);
-      mma_bf16_16x8x16(s1, a0, a1, a2, a3, b2, b3);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int row = g + ((i & 2) ? 8 : 0), col = 2 * c + (i & 1);
       sm.s[row][n0 + col] = n0 + col < n_here ? s0[i] * a.scale : -INFINITY;
-      sm.s[row][n0 + 8 + col] = n0 + 8 + col < n_here ? s1[i] * a.scale : -INFINITY;
     }
   }
   __syncthreads();
-  // ---- split-local softmax: warp w owns heads 4w .. 4w+3
-  for (int hh = 0; hh < 4; ++hh) {
-    const int h = warp * 4 + hh;
+  // ---- split-local softmax: warp w owns heads 2w, 2w+1
+  for (int hh = 0; hh < 2; ++hh) {
+    const int h = warp * 2 + hh;
     const float v0 = sm.s[h][lane], v1 = sm.s[h][lane + 32];
     const float m = warp_max(fmaxf(v0, v1));
     const float p0 = __expf(v0 - m), p1 = __expf(v1 - m);
@@ -164,7 +158,7 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
     }
   }
   __syncthreads();
-  // ---- O = P V: warp w owns latent dims 128w .. 128w+127 (16 tiles of 8)
+  // ---- O = P V: warp w owns latent dims 64w .. 64w+63 (8 tiles of 8)
   {
     uint32_t pa[4][4];
 #pragma unroll
@@ -176,8 +170,8 @@ __global__ __launch_bounds__(128) void sparse_mla_split_kernel(B200SparseMlaArgs
     }
     __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(a.part_o) + (((size_t)t * a.max_chunks + chunk) * H + hg * kMlaHeads) * kLat;
 #pragma unroll 2
-    for (int nt = 0; nt < 16; ++nt) {
-      const int n0 = warp * 128 + nt * 8;
+    for (int nt = 0; nt < 8; ++nt) {
+      const int n0 = warp * 64 + nt * 8;
       float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) {
@@ -271,8 +265,10 @@ cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  dim3 grid(a.max_chunks, a.rows);
-  launch_pdl(sparse_mla_split_kernel, grid, 128, sizeof(MlaSmem), s, a);
+  // up to four CTAs share a (row, chunk)'s entries and split its groups of 16 heads between them
+  const int hgs = a.heads / kMlaHeads;
+  dim3 grid(a.max_chunks, a.rows, hgs < 4 ? hgs : 4);
+  launch_pdl(sparse_mla_split_kernel, grid, 256, sizeof(MlaSmem), s, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dim3 grid2(a.heads, a.rows);
