@@ -306,7 +306,7 @@ def run_ours(args):
 
     # pinned host rows of the end-to-end steps
     hx = [x.cpu().pin_memory() for x in xs]
-    hout = torch.empty_like(hx[0]).pin_memory()
+    houts = [torch.empty_like(hx[0]).pin_memory() for _ in range(2)]  # results land alternately in two host buffers
     # one CUDA graph per (layer, input): a replay is one step with no host launch cost in the timed region
     stream = torch.cuda.Stream(dev)
     graphs, e2e_graphs = [], []
@@ -321,12 +321,14 @@ def run_ours(args):
             graphs.append(gr)
         # end-to-end steps: the copy of the step's rows from pinned host memory, the layer, the copy of the result
         # back to pinned host memory, as one graph (memcpy nodes at both ends)
-        for i in range(max(args.layers, n_in)):
+        n_e2e = max(args.layers, n_in)
+        n_e2e += n_e2e & 1  # even: step i always uses host buffer i % 2
+        for i in range(n_e2e):
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr, stream=stream):
                 x_in.copy_(hx[i % n_in], non_blocking=True)
                 run_step(layers[i % args.layers], x_in)
-                hout.copy_(out, non_blocking=True)
+                houts[i % 2].copy_(out, non_blocking=True)
             e2e_graphs.append(gr)
     # kernels per step: K1 9, K2i 2, K2: attention 2, projections and quants 3, exchanges 2, MoE block 5 (the
     # slot-ordered combine runs inside the second exchange)
@@ -362,9 +364,18 @@ def run_ours(args):
         raise SystemExit(f"a device wait gave up: status words {bad}")
 
     # ---- end to end: host rows in, host rows out, every step
+    # Every step copies its rows in from pinned host memory and its result out to pinned host memory.  The host reads
+    # step i - 1's result (from the other host buffer) after it has launched step i, so the read-back of one step and
+    # the launch of the next overlap, as they do when a serving loop walks the layers of a stack.
+    e2e_done = [torch.cuda.Event(), torch.cuda.Event()]
+    e2e_seen = []
+
     def e2e_step(i):
         e2e_graphs[i % len(e2e_graphs)].replay()  # H2D of this step's rows, the layer, D2H of its result
-        stream.synchronize()                      # the host has the result before the next step starts
+        e2e_done[i % 2].record(stream)
+        if i > 0:
+            e2e_done[(i - 1) % 2].synchronize()
+            e2e_seen.append(houts[(i - 1) % 2][0, 0].item())  # the host touches the previous step's result
 
     timed(e2e_step, args.warmup)
     e2e_us = timed(e2e_step, args.steps) * 1000.0 / args.steps
