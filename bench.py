@@ -215,14 +215,14 @@ def make_layer_weights(cfg, seed: int, device, rank: int = 0):
                         ffn=make_ffn_weights(cfg, seed, device, rank))
 
 
-def make_caches_and_step(cfg, device, seed=0):
+def make_caches_and_step(cfg, device, seed=0, headroom=0):
     """Random FP8 latent / FP4 index caches for every earlier position of the requests, a permuted page table
     (page 0 = pad page) and positions uniform in [ctx_lo, ctx_hi)."""
     from sgl_amd_mono_b200.layer import Caches, Step
 
     g = torch.Generator().manual_seed(9000 + seed)
     rows = cfg["rows"]
-    pos = torch.randint(cfg["ctx_lo"], cfg["ctx_hi"], (rows,), generator=g).to(torch.int32)
+    pos = torch.randint(cfg["ctx_lo"], cfg["ctx_hi"] - headroom, (rows,), generator=g).to(torch.int32)
     max_pages = (cfg["ctx_hi"] + 63) // 64
     n_pages = rows * max_pages + 1
     table = (torch.randperm(n_pages - 1, generator=g)[: rows * max_pages] + 1).view(rows, max_pages).to(torch.int32)
@@ -465,6 +465,140 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- the stack in one graph
+def run_stack(args):
+    """`--workload stack`: N distinct-weight layers of the same sparse-MLA FP8 MoE decoder chained inside ONE CUDA graph
+    per step kind (the 61-layer stack with its layer count scaled to what fits), a decode step of 8 rows and a
+    speculative-verify step of 8 requests x 4 draft tokens (32 rows, request r's rows at consecutive positions).  Every
+    layer has its own weights and its own KV / index caches; one exchange buffer serves the whole stack.  Reports the
+    per-layer time of the decode step as the metric, and both steps' latencies scaled to 61 layers with tokens/s."""
+    import torch.distributed as dist
+
+    import sgl_amd_mono_b200  # noqa: F401
+    from sgl_amd_mono_b200.layer import Caches, LayerBuild, LayerRunner, Step
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    cpu_group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        cpu_group = dist.new_group(backend="gloo")
+    tp = args.shard_of or world
+    requests, tokens = 8, 4
+    cfg = layer_cfg(requests, tp)
+    H = cfg["hidden"]
+    n_layers = args.stack_layers or (16 if tp >= 4 else 6)
+    caches0, step8, pos = make_caches_and_step(cfg, dev, headroom=tokens)  # room for the draft tokens' positions
+    table = step8.page_table
+    # verify rows: request r's draft token j sits at position pos[r] + j
+    vpos = (pos[:, None] + torch.arange(tokens, dtype=torch.int32)[None, :]).reshape(-1)
+    vreq = torch.arange(requests, dtype=torch.int32).repeat_interleave(tokens)
+    tb = table.cpu()
+    vslots = (tb[vreq.long(), (vpos // 64).long()].long() * 64 + (vpos % 64).long()).to(torch.int32)
+    step32 = Step(positions=vpos.to(dev), slots=vslots.to(dev), req_of_row=vreq.to(dev), ctx_len=(vpos + 1).to(torch.int32).to(dev),
+                  page_table=table)
+    build = LayerBuild(width=requests * tokens, tp=tp, max_ctx=cfg["ctx_hi"])
+    layers, reducer = [], None
+    for li in range(n_layers):
+        w = make_layer_weights(cfg, seed=li, device=dev, rank=rank)
+        c = caches0 if li == 0 else Caches(kv=caches0.kv.clone(), idx=caches0.idx.clone(), rope_table=caches0.rope_table)
+        r = LayerRunner(build, w, c, rank=rank, group=cpu_group, device=dev, reducer=reducer, world=world)
+        reducer = r.reducer
+        layers.append(r)
+    g = torch.Generator(device=dev).manual_seed(5)
+    x32 = torch.randn(requests * tokens, H, generator=g, device=dev).to(torch.bfloat16)
+    bufs = [torch.empty_like(x32), torch.empty_like(x32)]
+
+    def chain(rows, step):
+        x = x32[:rows]
+        for i, r in enumerate(layers):
+            o = bufs[i & 1][:rows]
+            r.forward(x, o, step)
+            x = o
+
+    stream = torch.cuda.Stream(dev)
+    graphs = {}
+    with torch.cuda.stream(stream):
+        for rows, st in ((requests, step8), (requests * tokens, step32)):
+            chain(rows, st)  # lazy initialisation outside capture
+            stream.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                chain(rows, st)
+            graphs[rows] = gr
+
+    def timed(gr, steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(steps):
+                gr.replay()
+            e1.record(stream)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() * 1000.0 / steps
+
+    steps = max(3, args.steps // n_layers)
+    res = {}
+    with clock_sampler(local) as cs:
+        for rows, gr in graphs.items():
+            timed(gr, max(3, args.warmup // n_layers))
+            res[rows] = timed(gr, steps)
+    clocks = cs.summary()
+    bad = [layers[0].reducer.status()] + [r.ffn.status() for r in layers] + [int(r.status[0].item()) for r in layers]
+    if any(bad):
+        raise SystemExit(f"a device wait gave up: status words {bad}")
+    peak, peak_kind = peaks()
+    per_layer = res[requests] / n_layers
+    by = layer_bytes(cfg, 57.0, int((pos + 1).sum()))
+    nvl = 2 * requests * H * 4 * (world - 1)
+    t_roof_us = (by["total"] / (peak * 1e9) + nvl / (NVLINK_GBS * 1e9)) * 1e6
+    result = {
+        "metric": METRIC, "value": round(per_layer, 3), "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": max(3, args.warmup // n_layers),
+        "ms_per_step": round(res[requests] / 1000.0, 6), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp8_e4m3 weights and KV, fp4_e2m1 index, f32 accumulate, bf16 rows", "data": "synthetic",
+        "config": {
+            "workload": f"stack of {n_layers} distinct-weight sparse-MLA FP8 MoE decoder layers in one CUDA graph, TP{tp}" +
+                        (f" (rank 0's shard alone on {world} GPU)" if args.shard_of else "") +
+                        "; decode step of 8 rows and verify step of 8 requests x 4 draft tokens (32 rows); the value is the decode "
+                        "step's time per layer",
+            "rows": requests, "tp": tp, "layers_in_graph": n_layers,
+            "l2": "every layer streams its own weights and caches, far more per step than L2 holds",
+            "launch": "one CUDA graph replay per step of the whole stack",
+        },
+        "stack": {
+            "decode_step_us": round(res[requests], 1), "verify_step_us": round(res[requests * tokens], 1),
+            "decode_us_per_layer": round(per_layer, 3), "verify_us_per_layer": round(res[requests * tokens] / n_layers, 3),
+            "decode_step_us_61_layers": round(per_layer * 61, 1),
+            "verify_step_us_61_layers": round(res[requests * tokens] / n_layers * 61, 1),
+            "decode_tokens_per_s_61_layers": round(requests / (per_layer * 61 * 1e-6), 1),
+            "verify_rows_per_s_61_layers": round(requests * tokens / (res[requests * tokens] / n_layers * 61 * 1e-6), 1),
+        },
+        "gpu_launches": 23 * n_layers * steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(by["total"] / (per_layer * 1e-6) / 1e9, 1), "peak": peak, "peak_kind": peak_kind,
+                     "unit": "GB/s", "frac": round(t_roof_us / per_layer, 4), "traffic": None,
+                     "kernel": "whole decode step (all kernels of a layer), algorithmic bytes at 57 distinct experts"},
+    }
+    if rank == 0:
+        print(json.dumps(result))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------------- CPU arm
 class CpuLayer:
     """The oracle's layer on the host cores, on a bounded sample.  Weights of the attention side and of
@@ -587,7 +721,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--layers", type=int, default=2, help="distinct-weight layers visited round-robin")
-    ap.add_argument("--workload", default="layer", choices=["layer", "ffn"])
+    ap.add_argument("--workload", default="layer", choices=["layer", "ffn", "stack"])
+    ap.add_argument("--stack-layers", type=int, default=0, help="layers in the stack graph (default: 16 at TP >= 4, else 6)")
     ap.add_argument("--shard-of", type=int, default=0, help="run rank 0's shard of a TP-<n> layer on one GPU (profiling)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
@@ -596,6 +731,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "stack":
+        run_stack(args)
     else:
         run_ours(args)
 
