@@ -214,7 +214,8 @@ class LayerRunner:
         a = self.a[:rows]
         self.reducer.run(self.attn_part[:rows], x, a, stream=st)
         inter_local = b.inter // b.tp
-        if rows <= 8 and inter_local % 256 == 0 and inter_local <= 2048:
+        persistent = inter_local % 256 == 0 and inter_local <= 2048  # shapes the persistent down projection takes
+        if rows <= 8 and persistent:
             # MoE block on the reduced stream; its slot-ordered combine is fused into the second all-reduce
             calls = self.ffn.stage_calls(a, out, None, False)
             for name, args in calls[:-1]:
@@ -228,13 +229,21 @@ class LayerRunner:
             contrib = self.ffn.scratch[L.contrib: L.contrib + slots * rows * b.hidden * 2].view(torch.bfloat16).view(
                 slots, rows, b.hidden)
             self.reducer.run(contrib, a, out, slots=slots, stream=st)
-        else:
-            # more than 8 rows (or an expert slice the persistent down projection does not take): the block combines its
-            # own slots into this rank's partial rows, which the second all-reduce then sums with the residual
-            part = self.ffn_part[:rows]
-            for name, args in self.ffn.stage_calls(a, part, None, False):
+            return
+        # Wider steps (a 32-row verify step): the block runs per group of 8 rows, each with its own routing union and
+        # the persistent kernels (32 rows pick nearly every expert, and four groups of 8 stream about as many expert
+        # slices as one pass over their union would), into this rank's partial rows; one all-reduce then sums them
+        # with the residual.  Shapes the persistent down projection does not take go through in one piece.
+        part = self.ffn_part[:rows]
+        group = 8 if persistent else rows
+        for r0 in range(0, rows, group):
+            r1 = min(rows, r0 + group)
+            calls = self.ffn.stage_calls(a[r0:r1], part[r0:r1], None, False)
+            if persistent:
+                calls[-1][1].variant = 2
+            for name, args in calls:
                 self.lib.call(name, args, self._s)
-            self.reducer.run(part, a, out, stream=st)
+        self.reducer.run(part, a, out, stream=st)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, step: Step, stream=None):
         """K1, K2i, K2.  With `overlap` (default) the indexer branch (KV / index records, index queries, scores, top-k)

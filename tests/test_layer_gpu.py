@@ -81,8 +81,10 @@ def test_layer_shard_against_oracle(lib, rows, tokens_per_request, ctx):
     assert torch.equal(r.a[:rows].cpu(), C.allreduce([r.attn_part[:rows]], x)), "residual stream after attention"
     ffn_ref = L.ffn_contrib(r.a[:rows], w, cfg)
     Lay = r.ffn.step_layout
-    ids = r.ffn.scratch[Lay.topk_ids: Lay.topk_ids + rows * cfg["topk"] * 4].view(torch.int32).view(rows, cfg["topk"]).cpu().numpy()
-    assert np.array_equal(ids, ffn_ref["ids"]), "routing"
+    # routing of the rows the block's scratch still holds (all of them, or the last group of 8 of a wide step)
+    n_last = rows if rows <= 8 else (rows - 1) % 8 + 1
+    ids = r.ffn.scratch[Lay.topk_ids: Lay.topk_ids + n_last * cfg["topk"] * 4].view(torch.int32).view(n_last, cfg["topk"]).cpu().numpy()
+    assert np.array_equal(ids, ffn_ref["ids"][rows - n_last:]), "routing"
     assert rel(out, C.allreduce([ffn_ref["out"]], r.a[:rows])) < 2e-2
 
     # ---- end to end from the same inputs
