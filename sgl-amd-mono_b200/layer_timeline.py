@@ -1,0 +1,81 @@
+"""Warm time of every launch of one decoder-layer step (the counterpart of the reference's per-stage kernel timers,
+test/kernels/deepseek_v41/time_layer.py): the C-ABI calls of `LayerRunner.forward` are recorded once, then each call
+is replayed 20 times inside a CUDA graph and timed with CUDA events.  Caches are warm and consecutive launches of one
+stage overlap their prologues, so the figures are lower bounds of what the stage costs inside the layer; the whole
+step's time comes from `bench.py`.
+
+    python sgl-amd-mono_b200/layer_timeline.py [tp]      # rank 0's shard of a TP-<tp> layer on one GPU (default 8)
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import sgl_amd_mono_b200  # noqa: E402,F401
+import bench  # noqa: E402
+from sgl_amd_mono_b200 import cabi  # noqa: E402
+from sgl_amd_mono_b200.layer import LayerBuild, LayerRunner  # noqa: E402
+
+
+def main():
+    lib = cabi.lib()
+    dev = torch.device("cuda", 0)
+    tp = int(sys.argv[1]) if len(sys.argv) > 1 else 8
+    cfg = bench.layer_cfg(8, tp)
+    caches, step, _ = bench.make_caches_and_step(cfg, dev)
+    w = bench.make_layer_weights(cfg, 0, dev)
+    r = LayerRunner(LayerBuild(width=8, tp=tp), w, caches, device=dev, world=1)
+    r.overlap = False  # one stream: the recorded order is the launch order
+    x = torch.randn(8, 7168, device=dev).bfloat16()
+    out = torch.empty_like(x)
+    calls = []
+    orig = lib.call
+
+    def rec(name, *args):
+        calls.append((name, args))
+        return orig(name, *args)
+
+    lib.call = rec
+    r.forward(x, out, step)
+    torch.cuda.synchronize()
+    lib.call = orig
+    s = torch.cuda.Stream(dev)
+    tot = 0.0
+    with torch.cuda.stream(s):
+        for name, args in calls:
+            if name == "moe_ffn_layout":
+                continue
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                for _ in range(20):
+                    orig(name, *args[:-1], s.cuda_stream)
+            g.replay()
+            s.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(s)
+            for _ in range(5):
+                g.replay()
+            e1.record(s)
+            s.synchronize()
+            us = e0.elapsed_time(e1) * 1000 / 100
+            tot += us
+            a = args[0]
+            extra = ""
+            if name == "gemv_fp8":
+                extra = f"n={a.n} k={a.k} groups={a.groups}"
+            elif name == "norm_quant":
+                extra = f"hidden={a.hidden}"
+            elif name == "quant128":
+                extra = f"rows={a.rows} cols={a.cols}"
+            elif name == "allreduce":
+                extra = f"slots={a.slots}"
+            print(f"{name:14s} {us:8.2f} us  {extra}")
+    print(f"sum {tot:.1f} us over {len(calls) - 1} launches")
+
+
+if __name__ == "__main__":
+    main()
