@@ -1,6 +1,6 @@
 // Sparse MLA decode over the selected FP8 latent entries (flash decoding, split + combine).
 //
-// Split: task = (row, chunk of 64 selected entries, up to four head slices); 8 warps; the slice's heads are taken
+// Split: task = (row, chunk of 64 selected entries, head slice); 8 warps; the slice's heads are taken
 //   16 at a time (one MMA M tile) over the same gathered entries.
 //   gather the 64 paged records, dequantise e4m3 * scale -> bf16 into shared memory,
 //   S = Q K^T on bf16 tensor cores (k = 512 latent + 64 position dims), split-local softmax
@@ -37,8 +37,13 @@ struct MlaSmem {
   float s[kMlaHeads][kChunkKeys];
 };
 
-__global__ __launch_bounds__(256) void sparse_mla_split_kernel(B200SparseMlaArgs a) {
+__global__ __launch_bounds__(256, 2) void sparse_mla_split_kernel(B200SparseMlaArgs a, unsigned long long* trace) {
   pdl_enter();
+  // timeline marks of CTA (0, 0, 0) when tracing is on: start, entries gathered, then per head group: queries loaded,
+  // scores, softmax, output
+  int tmark = 0;
+  const bool tr = trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+  if (tr) trace[tmark++] = globaltimer_ns();
   extern __shared__ __align__(16) uint8_t raw[];
   MlaSmem& sm = *reinterpret_cast<MlaSmem*>(raw);
   const int t = blockIdx.y, chunk = blockIdx.x;
@@ -51,6 +56,28 @@ __global__ __launch_bounds__(256) void sparse_mla_split_kernel(B200SparseMlaArgs
   const int req = a.req_of_row[t];
   const int* pages = a.page_table + (size_t)req * a.max_pages;
   const int* sel = a.topk_idx + (size_t)t * a.k + e0;
+
+  // the thread's share of a head group's queries: four 16-byte pieces of the latent part, one of the position part
+  uint4 qreg[5];
+  auto q_fetch = [&](int hg) {
+    const uint4* ql = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_lat) + ((size_t)t * H + hg * kMlaHeads) * kLat);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) qreg[k] = ql[threadIdx.x + 256 * k];
+    if (threadIdx.x < kMlaHeads * kRope / 8)
+      qreg[4] = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_rope) + ((size_t)t * H + hg * kMlaHeads) * kRope)[threadIdx.x];
+  };
+  auto q_store = [&]() {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = threadIdx.x + 256 * k, h = i / (kLat / 8), v = i % (kLat / 8);
+      *reinterpret_cast<uint4*>(&sm.q[h][v * 8]) = qreg[k];
+    }
+    if (threadIdx.x < kMlaHeads * kRope / 8) {
+      const int h = threadIdx.x / (kRope / 8), v = threadIdx.x % (kRope / 8);
+      *reinterpret_cast<uint4*>(&sm.q[h][kLat + v * 8]) = qreg[4];
+    }
+  };
+  q_fetch(blockIdx.z);  // in flight during the gather
 
   // ---- gather + dequantise: warp w (of 8) takes keys 8w .. 8w+7.  Lane j < 8 resolves key j's cache slot (selection
   // -> page table), then the eight records are fetched together so that their loads overlap.
@@ -95,29 +122,27 @@ __global__ __launch_bounds__(256) void sparse_mla_split_kernel(B200SparseMlaArgs
       if (lane < 8) *reinterpret_cast<uint4*>(&sm.rope[key][lane * 8]) = rope16[u];
     }
   }
+  if (tr) trace[tmark++] = globaltimer_ns();
   // the gathered entries serve every group of 16 heads this CTA takes (hg = blockIdx.z, + gridDim.z, ...)
   for (int hg = blockIdx.z; hg < H / kMlaHeads; hg += gridDim.z) {
-  // ---- queries: [16][512 latent | 64 position] bf16
-  {
-    const uint4* ql = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_lat) + ((size_t)t * H + hg * kMlaHeads) * kLat);
-    for (int i = threadIdx.x; i < kMlaHeads * kLat / 8; i += 256) {
-      const int h = i / (kLat / 8), v = i % (kLat / 8);
-      *reinterpret_cast<uint4*>(&sm.q[h][v * 8]) = ql[i];
-    }
-    const uint4* qr = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(a.q_rope) + ((size_t)t * H + hg * kMlaHeads) * kRope);
-    for (int i = threadIdx.x; i < kMlaHeads * kRope / 8; i += 256) {
-      const int h = i / (kRope / 8), v = i % (kRope / 8);
-      *reinterpret_cast<uint4*>(&sm.q[h][kLat + v * 8]) = qr[i];
-    }
-  }
+  // ---- queries: [16][512 latent | 64 position] bf16, fetched into registers one head group ahead
+  q_store();
   __syncthreads();
+  if (tr && tmark < 30) trace[tmark++] = globaltimer_ns();
+  if (hg + (int)gridDim.z < H / kMlaHeads) q_fetch(hg + gridDim.z);  // lands while this group is computed
 
-  // ---- S = Q K^T: warp w owns key tile w (8 keys)
+  // ---- S = Q K^T: warp w owns key tile w (8 keys).  Four accumulators take the k steps in turn: one accumulator
+  // would chain 36 MMAs through the tensor pipe's latency.
   {
-    float s0[4] = {0.f, 0.f, 0.f, 0.f};
+    float sa[4][4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sa[q][i] = 0.f;
     const int n0 = warp * 8;
-#pragma unroll 4
-    for (int k0 = 0; k0 < kLat + kRope; k0 += 16) {
+#pragma unroll
+    for (int ks = 0; ks < (kLat + kRope) / 16; ++ks) {
+      const int k0 = ks * 16;
       const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sm.q[g][k0 + 2 * c]);
       const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sm.q[g + 8][k0 + 2 * c]);
       const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sm.q[g][k0 + 2 * c + 8]);
@@ -131,15 +156,17 @@ __global__ __launch_bounds__(256) void sparse_mla_split_kernel(B200SparseMlaArgs
         b0 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + g][kr + 2 * c]);
         b1 = *reinterpret_cast<const uint32_t*>(&sm.rope[n0 + g][kr + 2 * c + 8]);
       }
-      mma_bf16_16x8x16(s0, a0, a1, a2, a3, b0, b1);
+      mma_bf16_16x8x16(sa[ks & 3], a0, a1, a2, a3, b0, b1);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
+      const float s0 = (sa[0][i] + sa[1][i]) + (sa[2][i] + sa[3][i]);
       const int row = g + ((i & 2) ? 8 : 0), col = 2 * c + (i & 1);
-      sm.s[row][n0 + col] = n0 + col < n_here ? s0[i] * a.scale : -INFINITY;
+      sm.s[row][n0 + col] = n0 + col < n_here ? s0 * a.scale : -INFINITY;
     }
   }
   __syncthreads();
+  if (tr && tmark < 30) trace[tmark++] = globaltimer_ns();
   // ---- split-local softmax: warp w owns heads 2w, 2w+1
   for (int hh = 0; hh < 2; ++hh) {
     const int h = warp * 2 + hh;
@@ -158,6 +185,7 @@ __global__ __launch_bounds__(256) void sparse_mla_split_kernel(B200SparseMlaArgs
     }
   }
   __syncthreads();
+  if (tr && tmark < 30) trace[tmark++] = globaltimer_ns();
   // ---- O = P V: warp w owns latent dims 64w .. 64w+63 (8 tiles of 8)
   {
     uint32_t pa[4][4];
@@ -169,23 +197,32 @@ __global__ __launch_bounds__(256) void sparse_mla_split_kernel(B200SparseMlaArgs
       pa[ks][3] = *reinterpret_cast<const uint32_t*>(&sm.p[g + 8][ks * 16 + 2 * c + 8]);
     }
     __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(a.part_o) + (((size_t)t * a.max_chunks + chunk) * H + hg * kMlaHeads) * kLat;
-#pragma unroll 2
-    for (int nt = 0; nt < 8; ++nt) {
-      const int n0 = warp * 64 + nt * 8;
-      float o[4] = {0.f, 0.f, 0.f, 0.f};
+    // eight independent accumulators (one per tile of 8 dims) advance together through the four k steps
+    float o[8][4];
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
         // V tile [16 keys][8 dims], row-major in shared memory: transpose on load
         uint32_t b0, b1;
-        const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&sm.lat[ks * 16 + (lane & 15)][n0]);
+        const uint32_t addr = (uint32_t)__cvta_generic_to_shared(&sm.lat[ks * 16 + (lane & 15)][warp * 64 + nt * 8]);
         ldmatrix_x2_trans(b0, b1, addr);
-        mma_bf16_16x8x16(o, pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b0, b1);
+        mma_bf16_16x8x16(o[nt], pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b0, b1);
       }
-      *reinterpret_cast<uint32_t*>(po + (size_t)g * kLat + n0 + 2 * c) = pack_bf16x2(o[0], o[1]);
-      *reinterpret_cast<uint32_t*>(po + (size_t)(g + 8) * kLat + n0 + 2 * c) = pack_bf16x2(o[2], o[3]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int n0 = warp * 64 + nt * 8;
+      *reinterpret_cast<uint32_t*>(po + (size_t)g * kLat + n0 + 2 * c) = pack_bf16x2(o[nt][0], o[nt][1]);
+      *reinterpret_cast<uint32_t*>(po + (size_t)(g + 8) * kLat + n0 + 2 * c) = pack_bf16x2(o[nt][2], o[nt][3]);
     }
   }
   __syncthreads();  // q, p and s are rewritten by the next group of heads
+  if (tr && tmark < 30) trace[tmark++] = globaltimer_ns();
   }
 }
 
@@ -265,10 +302,21 @@ cudaError_t launch_sparse_mla(const B200SparseMlaArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  // up to four CTAs share a (row, chunk)'s entries and split its groups of 16 heads between them
+  // CTAs that share a (row, chunk)'s entries split its groups of 16 heads between them; every CTA gathers the
+  // entries again (about as long as two head groups take), so the head groups are split only as far as it takes to
+  // fill the GPU once (two CTAs fit an SM)
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
   const int hgs = a.heads / kMlaHeads;
-  dim3 grid(a.max_chunks, a.rows, hgs < 4 ? hgs : 4);
-  launch_pdl(sparse_mla_split_kernel, grid, 256, sizeof(MlaSmem), s, a);
+  int hz = 2 * sms / (a.max_chunks * a.rows);
+  hz = hz < 1 ? 1 : (hz > hgs ? hgs : hz);
+  dim3 grid(a.max_chunks, a.rows, hz);
+  unsigned long long* tr = timeline_buffer() ? (unsigned long long*)timeline_buffer() + 8200 : nullptr;
+  launch_pdl(sparse_mla_split_kernel, grid, 256, sizeof(MlaSmem), s, a, tr);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dim3 grid2(a.heads, a.rows);
