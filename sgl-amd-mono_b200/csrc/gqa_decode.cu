@@ -145,26 +145,35 @@ __global__ __launch_bounds__(128) void gqa_split_kernel(B200GqaArgs a) {
       pa[ks][2] = *reinterpret_cast<const uint32_t*>(&sm.p[g][ks * 16 + 2 * c + 8]);
       pa[ks][3] = *reinterpret_cast<const uint32_t*>(&sm.p[g + 8][ks * 16 + 2 * c + 8]);
     }
-#pragma unroll 2
+    // one accumulator per tile of 8 dims; they advance together through the k steps, so that no MMA waits for the
+    // previous one's result (a chain through one accumulator runs at the tensor pipe's latency)
+    float o[D / 32][4];
+#pragma unroll
+    for (int nt = 0; nt < D / 32; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < kGqaChunk / 16; ++ks) {
+#pragma unroll
+      for (int nt = 0; nt < D / 32; ++nt) {
+        uint32_t b0, b1;
+        ldsm_x2_trans(b0, b1, (uint32_t)__cvta_generic_to_shared(&sm.v[ks * 16 + (lane & 15)][warp * (D / 4) + nt * 8]));
+        mma_bf16_k16(o[nt], pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b0, b1);
+      }
+    }
+#pragma unroll
     for (int nt = 0; nt < D / 32; ++nt) {
       const int n0 = warp * (D / 4) + nt * 8;
-      float o[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int ks = 0; ks < kGqaChunk / 16; ++ks) {
-        uint32_t b0, b1;
-        ldsm_x2_trans(b0, b1, (uint32_t)__cvta_generic_to_shared(&sm.v[ks * 16 + (lane & 15)][n0]));
-        mma_bf16_k16(o, pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b0, b1);
-      }
       // rows g and g+8 are query heads of the group
       if (g < G) {
         float* po = a.part_o + ((((size_t)t * a.q_heads + kvh * G + g) * a.max_chunks) + chunk) * D + n0 + 2 * c;
-        po[0] = o[0];
-        po[1] = o[1];
+        po[0] = o[nt][0];
+        po[1] = o[nt][1];
       }
       if (g + 8 < G) {
         float* po = a.part_o + ((((size_t)t * a.q_heads + kvh * G + g + 8) * a.max_chunks) + chunk) * D + n0 + 2 * c;
-        po[0] = o[2];
-        po[1] = o[3];
+        po[0] = o[nt][2];
+        po[1] = o[nt][3];
       }
     }
   }
