@@ -32,6 +32,7 @@ constexpr int kDownConsumers = 8;  // warps that share one stage
 constexpr int kDownGroups = 2;     // consumer groups; group g drains the stages it = g, g + kDownGroups, ..
 constexpr int kDownThreads = (kDownGroups * kDownConsumers + 1) * 32;
 constexpr int kDownRows = 16;
+constexpr int kDownRedFloats = 2 * kDownConsumers * 4 * 32;  // partials of one stage pair
 
 struct DownP {
   const uint8_t* midq;  // [cap][T][K]
@@ -55,8 +56,8 @@ __global__ __launch_bounds__(kDownThreads, 1) void down_stream_kernel(DownP p, c
   const int K = p.inter, T = p.rows, RB = p.rb, PP = p.pp;
   const int SB = RB * K;  // weights of a stage (a multiple of 128: K % 256 == 0)
   uint8_t* ring = smem;
-  float* red = reinterpret_cast<float*>(smem + (size_t)p.stages * SB);  // [groups][2 buffers][8 warps][4][32]
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + kDownGroups * 2 * kDownConsumers * 4 * 32);
+  float* red = reinterpret_cast<float*>(smem + (size_t)p.stages * SB);  // [groups][2 buffers][2 stages][8 warps][4][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + kDownGroups * 2 * kDownRedFloats);
   uint64_t* empty = full + p.stages;
   __shared__ int abort_flag;
   __shared__ int s_ids[520];
@@ -83,7 +84,8 @@ __global__ __launch_bounds__(kDownThreads, 1) void down_stream_kernel(DownP p, c
 
   const int nblk = p.hidden / RB;  // stages per expert
   const long long total = (long long)U * nblk;
-  const int su0 = (int)(total * blockIdx.x / gridDim.x), su1 = (int)(total * (blockIdx.x + 1) / gridDim.x);
+  // ranges are cut in pairs of stages (the consumers work through two stages of one expert per barrier)
+  const int su0 = 2 * (int)((total / 2) * blockIdx.x / gridDim.x), su1 = 2 * (int)((total / 2) * (blockIdx.x + 1) / gridDim.x);
   const int CB = K / p.ncopy;  // bytes of a box row
 
   if (warp == kDownGroups * kDownConsumers) {
@@ -117,17 +119,20 @@ __global__ __launch_bounds__(kDownThreads, 1) void down_stream_kernel(DownP p, c
   }
 
   // ---------------------------------------------------------------- consumers
-  // Group `grp` drains the stages it = grp, grp + kDownGroups, ..  A CTA's range of stages covers
-  // at most a few experts, and everything that depends only on the expert (this lane's activation
-  // fragment, its block scales, which slot of which row picked the expert, the route weights, the
-  // output addresses) is loaded when the expert changes and then stays in registers; per stage a
-  // warp fetches only its two weight block scales, one stage ahead.
+  // Group `grp` drains the stage pairs grp, grp + kDownGroups, ..  (a pair = two consecutive stages of one
+  // expert: the number of stages per expert is even and every CTA's range starts on a pair).  A CTA's range
+  // covers at most a few experts, and everything that depends only on the expert (this lane's activation
+  // fragment, its block scales, which slot of which row picked the expert, the route weight, the output
+  // address) is loaded when the expert changes and then stays in registers; per pair a warp fetches only its
+  // weight block scales, one pair ahead.  The K-split partials of a pair meet in shared memory behind ONE
+  // named barrier, and all eight warps of the group share the summing and the stores.
   const int grp = warp / kDownConsumers, wl = warp % kDownConsumers;
   const int g = lane >> 2, c4 = lane & 3;
   const int tl = wl / PP, kp = wl % PP;
-  const bool mine = tl * kDownRows < RB;  // (PP = 3 leaves two warps of a group idle)
+  const int TPS = RB / kDownRows;  // 16-row tiles per stage
+  const bool mine = tl < TPS;      // (PP = 3 leaves two warps of a group without MMA work)
   const int KB = K >> 7;
-  float* gred = red + grp * 2 * kDownConsumers * 4 * 32;
+  float* gred = red + grp * 2 * kDownRedFloats;
   bool dead = false;
   uint32_t frag_off[2];  // this lane's weight fragment inside a stage, per k block of its pair
 #pragma unroll
@@ -141,11 +146,16 @@ __global__ __launch_bounds__(kDownThreads, 1) void down_stream_kernel(DownP p, c
     o[0] = wrow[0];
     o[1] = wrow[1];
   };
+  // summing role (PP > 1): accumulator element `ei` of lane `lane`, for the (stage, tile) pairs wl / 4, wl / 4 + 2, ..
+  const int ei = wl & 3;
+  const int et = 2 * c4 + (ei & 1);            // row of the step
+  const int erow = g + ((ei & 2) ? 8 : 0);     // output row inside a tile
   // per-expert state
   int cur_u = -1;
   uint4 x[2][2];
-  float ms[2][2], wgt[2];
+  float ms[2][2], wgt[2], ewgt = 0.f;
   __nv_bfloat16* cptr[2];
+  __nv_bfloat16* ecol = nullptr;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     x[i][0] = x[i][1] = make_uint4(0, 0, 0, 0);
@@ -153,113 +163,158 @@ __global__ __launch_bounds__(kDownThreads, 1) void down_stream_kernel(DownP p, c
     wgt[i] = 0.f;
     cptr[i] = nullptr;
   }
-  int su = su0 + grp;
+  int su = su0 + 2 * grp;
   int u_c = su / nblk, blk_c = su % nblk;
-  float ws_cur[2] = {0.f, 0.f}, ws_nxt[2] = {0.f, 0.f};
-  if (mine && su < su1) load_ws(u_c, blk_c, ws_cur);
-  uint32_t n = 0;  // stages this group has drained
-  for (; su < su1; su += kDownGroups, ++n) {
-    // position of the group's next stage, without divisions
-    int u_n = u_c, blk_n = blk_c + kDownGroups;
+  int sa = (2 * grp) % S;  // ring slot and phase of the pair's first stage
+  uint32_t pha = ((2 * grp) / S) & 1;
+  float ws_cur[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, ws_nxt[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  if (mine && su < su1) {
+    load_ws(u_c, blk_c, ws_cur[0]);
+    load_ws(u_c, blk_c + 1, ws_cur[1]);
+  }
+  uint32_t n = 0;  // pairs this group has drained
+  for (; su < su1; su += 2 * kDownGroups, ++n) {
+    // position of the group's next pair, without divisions
+    int u_n = u_c, blk_n = blk_c + 2 * kDownGroups;
     while (blk_n >= nblk) {
       blk_n -= nblk;
       ++u_n;
     }
-    if (mine && su + kDownGroups < su1) load_ws(u_n, blk_n, ws_nxt);
-    if (mine && u_c != cur_u) {
+    if (mine && su + 2 * kDownGroups < su1) {
+      load_ws(u_n, blk_n, ws_nxt[0]);
+      load_ws(u_n, blk_n + 1, ws_nxt[1]);
+    }
+    if (u_c != cur_u) {
       cur_u = u_c;
-      if (g < T) {
-        const uint8_t* xr = p.midq + ((size_t)u_c * T + g) * K + kp * 256 + c4 * 32;
-        x[0][0] = ld_u4(xr);
-        x[0][1] = ld_u4(xr + 16);
-        x[1][0] = ld_u4(xr + 128);
-        x[1][1] = ld_u4(xr + 144);
-      }
+      if (mine) {
+        if (g < T) {
+          const uint8_t* xr = p.midq + ((size_t)u_c * T + g) * K + kp * 256 + c4 * 32;
+          x[0][0] = ld_u4(xr);
+          x[0][1] = ld_u4(xr + 16);
+          x[1][0] = ld_u4(xr + 128);
+          x[1][1] = ld_u4(xr + 144);
+        }
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int t = 2 * c4 + j;
-        ms[0][j] = ms[1][j] = 0.f;
-        wgt[j] = 0.f;
-        cptr[j] = nullptr;
-        if (t < T) {
-          const float* m = p.mids + ((size_t)u_c * T + t) * KB + kp * 2;
-          ms[0][j] = m[0];
-          ms[1][j] = m[1];
-          const int slot = p.pick[u_c * 32 + t];
+        for (int j = 0; j < 2; ++j) {
+          const int t = 2 * c4 + j;
+          ms[0][j] = ms[1][j] = 0.f;
+          wgt[j] = 0.f;
+          cptr[j] = nullptr;
+          if (t < T) {
+            const float* m = p.mids + ((size_t)u_c * T + t) * KB + kp * 2;
+            ms[0][j] = m[0];
+            ms[1][j] = m[1];
+            if (PP == 1) {
+              const int slot = p.pick[u_c * 32 + t];
+              if (slot) {
+                wgt[j] = s_w[t * 17 + slot - 1];
+                cptr[j] = p.contrib + ((size_t)(slot - 1) * T + t) * p.hidden + tl * kDownRows + g;
+              }
+            }
+          }
+        }
+      }
+      if (PP > 1) {
+        ewgt = 0.f;
+        ecol = nullptr;
+        if (et < T) {
+          const int slot = p.pick[u_c * 32 + et];
           if (slot) {
-            wgt[j] = s_w[t * 17 + slot - 1];
-            cptr[j] = p.contrib + ((size_t)(slot - 1) * T + t) * p.hidden + tl * kDownRows + g;
+            ewgt = s_w[et * 17 + slot - 1];
+            ecol = p.contrib + ((size_t)(slot - 1) * T + et) * p.hidden + erow;
           }
         }
       }
     }
     const uint32_t it = (uint32_t)(su - su0);
-    const int s = it % S;
-    const uint32_t ph = (it / S) & 1;
     const bool tr = p.trace && blockIdx.x < 4 && it < 256 && threadIdx.x == 0;
     unsigned long long* trow = p.trace + ((size_t)blockIdx.x * 256 + (it & 255)) * 8;
     if (tr) trow[2] = globaltimer_ns();
-    if (!__all_sync(0xffffffffu, mbar_wait(&full[s], ph, ctx, 4))) {
-      dead = true;
-      if (PP == 1) return;  // no named barriers on this path: a warp may leave alone
-    }
-    if (tr) trow[3] = globaltimer_ns();
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    if (!dead && mine) {
-      const uint32_t st = smem_u32(ring + (size_t)s * SB);
-      // per k block: four independent MMAs (a chain through one accumulator would serialise on
-      // the tensor pipe's latency), summed pairwise, then the block scale
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-      for (int kbi = 0; kbi < 2; ++kbi) {
-        const uint32_t lo_addr = st + frag_off[kbi];
-        const uint32_t hi_addr = lo_addr + 8 * CB;
-        const uint4 lo0 = lds_u4(lo_addr), lo1 = lds_u4(lo_addr + 16);
-        const uint4 hi0 = lds_u4(hi_addr), hi1 = lds_u4(hi_addr + 16);
-        const uint4 x0 = x[kbi][0], x1 = x[kbi][1];
-        float q0[4] = {0.f, 0.f, 0.f, 0.f}, q1[4] = {0.f, 0.f, 0.f, 0.f}, q2[4] = {0.f, 0.f, 0.f, 0.f},
-              q3[4] = {0.f, 0.f, 0.f, 0.f};
-        mma_e4m3_16x8x32(q0, lo0.x, hi0.x, lo0.y, hi0.y, x0.x, x0.y);
-        mma_e4m3_16x8x32(q1, lo0.z, hi0.z, lo0.w, hi0.w, x0.z, x0.w);
-        mma_e4m3_16x8x32(q2, lo1.x, hi1.x, lo1.y, hi1.y, x1.x, x1.y);
-        mma_e4m3_16x8x32(q3, lo1.z, hi1.z, lo1.w, hi1.w, x1.z, x1.w);
-        const float f0 = ws_cur[kbi] * ms[kbi][0], f1 = ws_cur[kbi] * ms[kbi][1];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[i] = fmaf((q0[i] + q1[i]) + (q2[i] + q3[i]), (i & 1) ? f1 : f0, acc[i]);
+    for (int st = 0; st < 2; ++st) {
+      int s = sa + st;
+      uint32_t ph = pha;
+      if (s == S) {
+        s = 0;
+        ph ^= 1u;
       }
+      if (!dead && !__all_sync(0xffffffffu, mbar_wait(&full[s], ph, ctx, 4))) dead = true;
+      if (dead) {
+        if (PP == 1) return;  // no named barriers on this path: a warp may leave alone
+        continue;
+      }
+      if (tr && st == 0) trow[3] = globaltimer_ns();
+      if (mine) {
+        const uint32_t stg = smem_u32(ring + (size_t)s * SB);
+        // per k block: four independent MMAs (a chain through one accumulator would serialise on
+        // the tensor pipe's latency), summed pairwise, then the block scale
+#pragma unroll
+        for (int kbi = 0; kbi < 2; ++kbi) {
+          const uint32_t lo_addr = stg + frag_off[kbi];
+          const uint32_t hi_addr = lo_addr + 8 * CB;
+          const uint4 lo0 = lds_u4(lo_addr), lo1 = lds_u4(lo_addr + 16);
+          const uint4 hi0 = lds_u4(hi_addr), hi1 = lds_u4(hi_addr + 16);
+          const uint4 x0 = x[kbi][0], x1 = x[kbi][1];
+          float q0[4] = {0.f, 0.f, 0.f, 0.f}, q1[4] = {0.f, 0.f, 0.f, 0.f}, q2[4] = {0.f, 0.f, 0.f, 0.f},
+                q3[4] = {0.f, 0.f, 0.f, 0.f};
+          mma_e4m3_16x8x32(q0, lo0.x, hi0.x, lo0.y, hi0.y, x0.x, x0.y);
+          mma_e4m3_16x8x32(q1, lo0.z, hi0.z, lo0.w, hi0.w, x0.z, x0.w);
+          mma_e4m3_16x8x32(q2, lo1.x, hi1.x, lo1.y, hi1.y, x1.x, x1.y);
+          mma_e4m3_16x8x32(q3, lo1.z, hi1.z, lo1.w, hi1.w, x1.z, x1.w);
+          const float f0 = ws_cur[st][kbi] * ms[kbi][0], f1 = ws_cur[st][kbi] * ms[kbi][1];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            acc[st][i] = fmaf((q0[i] + q1[i]) + (q2[i] + q3[i]), (i & 1) ? f1 : f0, acc[st][i]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
     }
-    __syncwarp();
-    if (!dead && lane == 0) mbar_arrive(&empty[s]);
     if (tr) trow[4] = globaltimer_ns();
 
     if (PP > 1) {
-      // partials of one tile meet in pair order; two buffers, so one barrier per stage is enough
-      float* rb = gred + (n & 1) * kDownConsumers * 4 * 32;
+      // partials [stage of the pair][warp][element][lane]; two buffers, so one barrier per pair is enough
+      float* rb = gred + (n & 1) * kDownRedFloats;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) rb[(wl * 4 + i) * 32 + lane] = acc[i];
+      for (int st = 0; st < 2; ++st)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rb[((st * kDownConsumers + wl) * 4 + i) * 32 + lane] = acc[st][i];
       // every consumer of the group takes the same exit: the barrier also ORs the "a wait gave up" bits
       if (named_bar_or(2 + grp, kDownConsumers * 32, dead)) return;
-      if (kp == 0 && mine) {  // (an idle leader's partners would lie past the buffer)
+      // the partials of one tile are summed in k order
+      for (int q = wl; q < 2 * TPS * 4; q += kDownConsumers) {
+        const int tt = q >> 2;
+        const int st = tt >= TPS ? 1 : 0, tile = tt - st * TPS;
+        const float* src = rb + ((st * kDownConsumers + tile * PP) * 4 + ei) * 32 + lane;
+        float v = src[0];
+        for (int k2 = 1; k2 < PP; ++k2) v += src[k2 * 128];
+        if (ecol) ecol[(size_t)(blk_c + st) * RB + tile * kDownRows] = __float2bfloat16_rn(__fmul_rn(v, ewgt));
+      }
+    } else if (mine) {
+#pragma unroll
+      for (int st = 0; st < 2; ++st) {
+        const int row0 = (blk_c + st) * RB;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          float v = acc[i];
-          for (int k2 = 1; k2 < PP; ++k2) v += rb[((wl + k2) * 4 + i) * 32 + lane];
-          acc[i] = v;
+          const int j = i & 1;
+          if (cptr[j]) cptr[j][row0 + ((i & 2) ? 8 : 0)] = __float2bfloat16_rn(__fmul_rn(acc[st][i], wgt[j]));
         }
-      }
-    }
-    if (mine && kp == 0) {
-      const int row0 = blk_c * RB;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int j = i & 1;
-        if (cptr[j]) cptr[j][row0 + ((i & 2) ? 8 : 0)] = __float2bfloat16_rn(__fmul_rn(acc[i], wgt[j]));
       }
     }
     if (tr) trow[5] = globaltimer_ns();
     u_c = u_n;
     blk_c = blk_n;
-    ws_cur[0] = ws_nxt[0];
-    ws_cur[1] = ws_nxt[1];
+#pragma unroll
+    for (int st = 0; st < 2; ++st) {
+      ws_cur[st][0] = ws_nxt[st][0];
+      ws_cur[st][1] = ws_nxt[st][1];
+    }
+    sa += 2 * kDownGroups;
+    while (sa >= S) {
+      sa -= S;
+      pha ^= 1u;
+    }
   }
 }
 
@@ -308,7 +363,7 @@ bool down_stream_ok(const B200MoeDownArgs& a) {
   if (a.rows > 8 || a.inter % 256 != 0 || KB / 2 > 8 || a.experts + 1 > 520 || a.topk > 16) return false;
   const int ncopy = (a.inter + 1023) / 1024;
   const int rb = 8 / (a.inter / 256) * kDownRows;
-  if (a.inter % (ncopy * 16) != 0 || a.hidden % rb != 0) return false;
+  if (a.inter % (ncopy * 16) != 0 || a.hidden % (2 * rb) != 0) return false;
   return true;
 }
 
@@ -335,8 +390,8 @@ cudaError_t launch_moe_down_stream(const B200MoeDownArgs& a, void* contrib, uint
   p.status = status;
   p.trace = (unsigned long long*)timeline_buffer();
   const int SB = p.rb * a.inter;
-  const size_t fixed = kDownGroups * 2 * kDownConsumers * 4 * 32 * sizeof(float) + 256;
-  const size_t budget = 220 * 1024;
+  const size_t fixed = kDownGroups * 2 * kDownRedFloats * sizeof(float) + 128;
+  const size_t budget = 6 * 32768 + fixed;  // six 32 KiB stages (227 KiB per CTA, less the static arrays)
   int stages = (int)((budget - fixed) / SB);
   if (stages > 8) stages = 8;
   if (stages < 2) return cudaErrorInvalidValue;

@@ -7,7 +7,8 @@ the launching stream, median of `--reps`.  Prints one JSON line per stage with i
 Stages: gqa (dense GQA decode: 8 rows, contexts uniform in [1024, 32768), 8 query heads on 1 KV head, d = 128, and
 16 on 2 with d = 256 at context 8192), gdn (verify chain: 8 requests x 4 tokens, 16 key / 32 value heads; decode:
 8 requests), index (index scores, 8 rows, contexts in [4096, 65536), both kernels), topk (exact top-2048 of them),
-mx4 (MXFP4 experts on MXFP8 rows: gate/up and down + combine at the two MXFP4 layers' per-rank shapes).
+mx4 (MXFP4 experts on MXFP8 rows: gate/up and down + combine at the two MXFP4 layers' per-rank shapes), down (opt-in:
+the FP8 expert down projection alone at whole-width expert slices, the case its ncu capture runs).
 """
 
 from __future__ import annotations
@@ -182,6 +183,36 @@ def bench_mx4(lib, reps, flush):
         report(name + " down+combine", us, cap * per, distinct_experts=cap)
 
 
+def bench_down(lib, reps, flush):
+    """FP8 block-scaled expert down projection alone (persistent TMA-ring kernel, contributions only): 8 rows, whole-width
+    expert slices (hidden 7168, inter 2048) of 48 distinct experts + the shared one out of 64 resident: 0.72 GB streamed
+    of 0.95 GB held."""
+    g = torch.Generator().manual_seed(11)
+    H, I, E, K, rows, U = 7168, 2048, 64, 8, 8, 48
+    w2 = torch.randint(0, 120, ((E + 1) * H, I), generator=g, dtype=torch.uint8).to(DEV)
+    w2s = torch.rand(E + 1, H // 128, I // 128, generator=g).to(DEV)
+    ids = torch.randperm(E, generator=g)[:U].sort().values
+    uids = torch.cat([ids, torch.tensor([E])]).to(torch.int32).to(DEV)
+    cap = rows * K + 1
+    ucount = torch.tensor([U + 1], dtype=torch.int32, device=DEV)
+    pick = torch.zeros(cap, 32, dtype=torch.uint8)
+    for i in range(U):
+        pick[i, i % rows] = i // rows + 1
+    pick[U, :rows] = K + 1
+    pick = pick.to(DEV)
+    mq = torch.randint(0, 120, (cap, rows, I), generator=g, dtype=torch.uint8).to(DEV)
+    ms = torch.rand(cap, rows, I // 128, generator=g).to(DEV)
+    wts = torch.rand(rows, K, generator=g).to(DEV)
+    contrib = torch.zeros(K + 1, rows, H, dtype=torch.bfloat16, device=DEV)
+    out = torch.empty(rows, H, dtype=torch.bfloat16, device=DEV)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    dn = cabi.fill("B200MoeDownArgs", midq=mq, mid_scale=ms, w2=w2, w2_scale=w2s, union_count=ucount, union_ids=uids, union_pick=pick,
+                   topk_w=wts, residual=None, out=out, rows=rows, hidden=H, inter=I, experts=E, topk=K, has_shared=1, contrib=contrib,
+                   status=st, union_cap=cap, variant=2, skip_combine=1)
+    us = timed(lambda: lib.call("moe_down", dn, stream()), reps, flush)
+    report("fp8 experts down h7168 i2048, persistent kernel", us, (U + 1) * H * I, distinct_experts=U + 1, status=int(st.item()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--stages", default="gqa,gdn,index,topk,mx4")
@@ -196,6 +227,8 @@ def main():
         bench_gdn(lib, args.reps, flush)
     if "mx4" in stages:
         bench_mx4(lib, args.reps, flush)
+    if "down" in stages:
+        bench_down(lib, args.reps, flush)
     if "index" in stages or "topk" in stages:
         bench_index(lib, args.reps, flush, "topk" in stages)
 
