@@ -226,6 +226,17 @@ def test_c1_block_against_oracle(lib):
     assert e < 5e-3, e
 
 
+@pytest.mark.parametrize("inter", [256, 512, 1024, 2048])
+def test_block_at_every_expert_width(lib, inter):
+    """The persistent down projection splits K over 1, 2, 4 or 8 warps per 16-row tile depending on the expert
+    width (the per-rank widths of the sparse-MLA MoE layer at TP8, 4, 2 and 1): every split against the oracle."""
+    cfg = dict(inputs.C1, name=f"c1_i{inter}", inter=inter, experts=16, rows=8)
+    w = inputs.moe_weights(cfg, seed=3, device=DEV)
+    x = inputs.rows_bf16(8, cfg["hidden"], seed=4).to(DEV)
+    out, o, e = _check_block(cfg, w, x)
+    assert e < 6e-3, e
+
+
 def test_c1_block_residual_width_and_row_independence(lib):
     cfg = inputs.C1
     w = inputs.moe_weights(cfg, seed=1, device=DEV)
