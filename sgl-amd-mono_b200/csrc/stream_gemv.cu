@@ -361,11 +361,11 @@ bool make_map_u32(CUtensorMap* m, const void* base, uint64_t cols, uint64_t rows
 }
 
 template <int NT, int MODE>
-static cudaError_t launch_stream_nt(StreamP p, int grid, long long w_rows, cudaStream_t s) {
+static cudaError_t launch_stream_nt(StreamP p, int grid, long long w_rows, cudaStream_t s, int max_stages) {
   const size_t budget = 225 * 1024;
   const size_t fixed = 2 * red_floats<NT>() * sizeof(float) + 256;
   int stages = (int)((budget - fixed) / stage_bytes<NT>());
-  if (stages > 8) stages = 8;
+  if (stages > max_stages) stages = max_stages;
   p.stages = stages;
   const size_t smem = (size_t)stages * stage_bytes<NT>() + fixed;
   static bool configured = false;
@@ -389,10 +389,10 @@ static cudaError_t launch_stream_nt(StreamP p, int grid, long long w_rows, cudaS
 }
 
 template <int MODE>
-static cudaError_t launch_stream(const StreamP& p, int grid, long long w_rows, cudaStream_t s) {
-  if (p.rows <= 8) return launch_stream_nt<1, MODE>(p, grid, w_rows, s);
-  if (p.rows <= 16) return launch_stream_nt<2, MODE>(p, grid, w_rows, s);
-  return launch_stream_nt<4, MODE>(p, grid, w_rows, s);
+static cudaError_t launch_stream(const StreamP& p, int grid, long long w_rows, cudaStream_t s, int max_stages = 8) {
+  if (p.rows <= 8) return launch_stream_nt<1, MODE>(p, grid, w_rows, s, max_stages);
+  if (p.rows <= 16) return launch_stream_nt<2, MODE>(p, grid, w_rows, s, max_stages);
+  return launch_stream_nt<4, MODE>(p, grid, w_rows, s, max_stages);
 }
 
 static int sm_count() {
@@ -446,8 +446,16 @@ cudaError_t launch_gemv_stream(const B200GemvFp8Args& a, uint32_t* status, cudaS
   p.tiles = (a.n + 31) / 32;
   p.status = status;
   int grid = sm_count();
-  if (p.tiles < grid) grid = p.tiles;
-  return launch_stream<MODE_PLAIN>(p, grid, a.n, s);
+  int max_stages = 8;
+  if (p.tiles < grid) {
+    grid = p.tiles;
+  } else if (a.rows <= 8 && p.tiles > grid && p.tiles <= 2 * grid) {
+    // between one and two units per SM: a second round would leave half of the SMs idle, so every unit gets its own
+    // CTA and two CTAs with two-stage rings share an SM
+    grid = p.tiles;
+    max_stages = 2;
+  }
+  return launch_stream<MODE_PLAIN>(p, grid, a.n, s, max_stages);
 }
 
 }  // namespace b200mono
